@@ -47,8 +47,10 @@ def get_architecture(name: str) -> Architecture:
 
 def config_from_dict(raw: dict) -> tuple[Architecture, ModelConfig]:
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):  # some designs name themselves with one string
+        names = [raw["architecture"]]
     if not isinstance(names, list) or not names or not isinstance(names[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' a name)")
     arch = get_architecture(names[0])
     return arch, arch.config_class.from_dict(raw)
 

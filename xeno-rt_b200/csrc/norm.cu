@@ -106,8 +106,46 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
     dst[c] = from_float<TO>((xr[c] * inv) * to_float(w[c]));
 }
 
+// Layer norm with a weight and no bias: y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, any width.
+// Two sums over the row in a fixed order (the mean first, then the squared deviations from it).
+template <typename TW, typename TO>
+__global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
+                                 const int* __restrict__ rows, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows != nullptr ? rows[r] : r;
+  const float* xr = x + (size_t)src * width;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) acc += xr[c];
+  const float mean = block_sum(acc, scratch) / (float)width;
+  acc = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float d = xr[c] - mean;
+    acc = fmaf(d, d, acc);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  TO* dst = out + (size_t)r * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    dst[c] = from_float<TO>(((xr[c] - mean) * inv) * to_float(w[c]));
+}
+
 }  // namespace xrt
 
+
+XRT_EXPORT int xrt_layernorm(void* out, const float* x, const void* weight, const int* rows, int n_rows,
+                             int width, float eps, int weight_dtype, int out_dtype, cudaStream_t stream) {
+  if (n_rows < 0 || width <= 0) return XRT_ERR_ARGUMENT;
+  if (n_rows == 0) return XRT_OK;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+  XRT_DISPATCH_DTYPE(weight_dtype, TW, {
+    XRT_DISPATCH_DTYPE(out_dtype, TO, {
+      xrt::launch_kernel(xrt::layernorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
+    });
+  });
+  return xrt::launch_status();
+}
 
 XRT_EXPORT int xrt_rmsnorm(void* out, const float* x, const void* weight, const int* rows, int n_rows,
                            int width, float eps, int weight_dtype, int out_dtype, cudaStream_t stream) {

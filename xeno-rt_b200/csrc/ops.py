@@ -28,7 +28,18 @@ _CODES = {torch.float32: 0, torch.bfloat16: 1}
 _SIGNATURES = {
     "xrt_embedding": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     "xrt_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
+    "xrt_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _P],
+    "xrt_rotation_table": [_P, _P, _P, _F, _I, _I, _P],
+    "xrt_state_scan": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "xrt_short_conv": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_decay": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
+    "xrt_unit_heads": [_P, _I, _I, _I, _I, _F, _I, _F, _P],
+    "xrt_head_norm_gate": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "xrt_gate_mul": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_rms_scale_add": [_P, _P, _P, _I, _I, _F, _F, _P],
+    "xrt_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
+    "xrt_scale_softcap": [_P, _I, _I, _F, _F, _P],
     "xrt_rope_table": [_P, _P, _P, _F, _I, _I, _P],
     "xrt_qk_rope_kv_write": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                              _I, _I, _I, _I, _I, _P],
@@ -238,6 +249,18 @@ def rmsnorm(out, x, weight, eps: float, rows=None) -> None:
     _check(_kernels().xrt_rmsnorm(_ptr(out, "out"), _ptr(x, "x", torch.float32), _ptr(weight, "weight"),
                                  _ptr(rows, "rows", torch.int32), n_rows, width, float(eps),
                                  _code(weight.dtype), _code(out.dtype), _stream()), "rmsnorm")
+
+
+def layernorm(out, x, weight, eps: float, rows=None) -> None:
+    """out[r] = (x[r] - mean) / sqrt(variance + eps) * weight (rows gathered through ``rows`` if given); x is float32."""
+    n_rows, width = out.shape
+    if x.shape[1] != width or weight.numel() != width or (rows is None and x.shape[0] != n_rows):
+        raise KernelError("layernorm: shapes do not fit")
+    if rows is not None and rows.numel() != n_rows:
+        raise KernelError("layernorm: one row index per output row is needed")
+    _check(_kernels().xrt_layernorm(_ptr(out, "out"), _ptr(x, "x", torch.float32), _ptr(weight, "weight"),
+                                   _ptr(rows, "rows", torch.int32), n_rows, width, float(eps),
+                                   _code(weight.dtype), _code(out.dtype), _stream()), "layernorm")
 
 
 def swiglu(out, gate_up) -> None:
@@ -694,3 +717,140 @@ def mark_seen(seen, slots, ids, vocab: int) -> None:
     _check(_kernels().xrt_mark_seen(_ptr(seen, "seen", torch.int32), seen.shape[1],
                                    _ptr(slots, "slots", torch.int32), _ptr(ids, "ids", torch.int32), n, vocab,
                                    _stream()), "mark_seen")
+
+
+# ---------------------------------------------------------------------------------------------------
+# Mixers with a matrix state, and the small steps around them (csrc/state_mixers.cu)
+_ACTS = {None: 0, "none": 0, "silu": 1, "sigmoid": 2}
+
+
+def _columns(t, name: str, width: int):
+    """Pointer and row stride of a float32 tensor [T, >= width] whose rows may be a slice of wider rows."""
+    if t.dim() != 2 or t.dtype != torch.float32 or t.stride(1) != 1 or t.shape[1] < width or not t.is_cuda:
+        raise KernelError(f"{name} must be float32 rows of at least {width} columns on the device")
+    return t.data_ptr(), t.stride(0)
+
+
+def rotation_table(cos_sin, positions, freq, magnitude: float = 1.0) -> None:
+    """cos_sin[t, i] = magnitude * (cos, sin)(positions[t] * freq[i]); cos_sin is float32 [T, half, 2]."""
+    n, half = cos_sin.shape[0], cos_sin.shape[1]
+    if positions.numel() != n or freq.numel() != half or cos_sin.shape[2] != 2:
+        raise KernelError("rotation_table: shapes do not fit")
+    _check(_kernels().xrt_rotation_table(_ptr(cos_sin, "cos_sin", torch.float32),
+                                        _ptr(positions, "positions", torch.int32), _ptr(freq, "freq", torch.float32),
+                                        float(magnitude), n, half, _stream()), "rotation_table")
+
+
+def state_scan(out, q, k, v, decay, beta, state, cu_seqlens, seq_slot, n_heads: int, n_qk_heads: int, dim: int,
+               vdim: int, q_scale: float = 1.0, delta: bool = False) -> None:
+    """The scan of a matrix state over the step's tokens, a sequence after the other in parallel:
+    S <- diag(decay_t) S + k_t u_t^T and out_t = S^T (q_t * q_scale), with u_t = v_t, or with ``delta``
+    u_t = sigmoid(beta_t) (v_t - S^T k_t) taken after the decay.  q, k [T, n_qk_heads * dim], v [T, n_heads * vdim],
+    decay [T, n_heads * dim] (rows may be slices of wider rows), beta [T, n_heads] before its sigmoid, all
+    float32; ``state`` float32 [slots, n_heads, vdim, dim] is read and left as the sequences' last state."""
+    n = out.shape[0]
+    if out.shape != (n, n_heads * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("state_scan: out must be float32 [T, heads * vdim]")
+    if state.dim() != 4 or tuple(state.shape[1:]) != (n_heads, vdim, dim) or state.dtype != torch.float32:
+        raise KernelError("state_scan: the state must be float32 [slots, heads, vdim, dim]")
+    for t in (q, k, v, decay) + ((beta,) if delta else ()):
+        if t.shape[0] != n:
+            raise KernelError("state_scan: one row a token is needed")
+    qp, qs = _columns(q, "q", n_qk_heads * dim)
+    kp, ks = _columns(k, "k", n_qk_heads * dim)
+    vp, vs = _columns(v, "v", n_heads * vdim)
+    dp, ds = _columns(decay, "decay", n_heads * dim)
+    bp, bs = _columns(beta, "beta", n_heads) if delta else (0, 0)
+    n_seqs = seq_slot.numel()
+    if cu_seqlens.numel() != n_seqs + 1:
+        raise KernelError("state_scan: cu_seqlens must hold one entry more than seq_slot")
+    _check(_kernels().xrt_state_scan(_ptr(out, "out"), qp, qs, kp, ks, vp, vs, dp, ds, bp, bs, _ptr(state, "state"),
+                                    _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
+                                    n_seqs, n_heads, n_qk_heads, dim, vdim, float(q_scale), 1 if delta else 0, _stream()),
+           "state_scan")
+
+
+def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: str = "silu") -> None:
+    """out[t, c] = act(sum_j weight[c, j] * x[t - (taps - 1) + j, c]) inside each sequence; inputs before the
+    step come from ``state`` [slots, taps - 1, channels] (zeros at a sequence's start), which is left holding
+    the sequence's last taps - 1 inputs.  x: float32 rows of at least ``channels`` columns; all float32."""
+    n, channels = out.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or x.shape[0] != n or out.dtype != torch.float32:
+        raise KernelError("short_conv: shapes do not fit")
+    if taps > 1 and (state.dim() != 3 or tuple(state.shape[1:]) != (taps - 1, channels)):
+        raise KernelError("short_conv: the state must be [slots, taps - 1, channels]")
+    xp, xs = _columns(x, "x", channels)
+    n_seqs = seq_slot.numel()
+    _check(_kernels().xrt_short_conv(_ptr(out, "out"), xp, xs, _ptr(weight, "weight", torch.float32),
+                                    _ptr(state if taps > 1 else None, "state", torch.float32),
+                                    _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
+                                    n_seqs, int(max_new), channels, taps, _ACTS[act], _stream()), "short_conv")
+    if taps > 1:
+        add_launches(1)
+
+
+def decay_from_gate(a, bias, n_heads: int, dim: int, tau: float) -> None:
+    """a <- sigmoid(a + bias)^(1 / tau) in place; a float32 [T, n_heads * dim]."""
+    _check(_kernels().xrt_decay(_ptr(a, "a", torch.float32), _ptr(bias, "bias", torch.float32), 0, a.shape[0], n_heads,
+                               dim, 0, float(tau), _stream()), "decay_from_gate")
+
+
+def decay_from_step(a, bias, a_log, n_heads: int, dim: int) -> None:
+    """a <- exp(-exp(a_log[head]) * softplus(a + bias)) in place; a float32 [T, n_heads * dim]."""
+    if a_log.numel() != n_heads:
+        raise KernelError("decay_from_step: one a_log a head is needed")
+    _check(_kernels().xrt_decay(_ptr(a, "a", torch.float32), _ptr(bias, "bias", torch.float32),
+                               _ptr(a_log, "a_log", torch.float32), a.shape[0], n_heads, dim, 1, 1.0, _stream()),
+           "decay_from_step")
+
+
+def unit_heads(x, n_heads: int, dim: int, eps: float, scaled_heads: int = 0, scale: float = 1.0) -> None:
+    """Every head of the first n_heads * dim columns of x (float32 rows) becomes x / sqrt(sum(x^2) + eps), the
+    first ``scaled_heads`` of them times ``scale``; in place."""
+    xp, xs = _columns(x, "x", n_heads * dim)
+    _check(_kernels().xrt_unit_heads(xp, xs, x.shape[0], n_heads, dim, float(eps), int(scaled_heads), float(scale),
+                                    _stream()), "unit_heads")
+
+
+def head_norm_gate(y, o, weight, gate, n_heads: int, vdim: int, eps: float, act: str) -> None:
+    """y[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]); o float32 [T, heads * vdim]."""
+    n = o.shape[0]
+    if y.shape != (n, n_heads * vdim) or o.shape != y.shape or weight.numel() != vdim or gate.shape[0] != n:
+        raise KernelError("head_norm_gate: shapes do not fit")
+    gp, gs = _columns(gate, "gate", n_heads * vdim)
+    _check(_kernels().xrt_head_norm_gate(_ptr(y, "y"), _ptr(o, "o", torch.float32), _ptr(weight, "weight", torch.float32),
+                                        gp, gs, n, n_heads, vdim, float(eps), _ACTS[act], _code(y.dtype), _stream()),
+           "head_norm_gate")
+
+
+def gate_mul(x, gate, act: str = "sigmoid") -> None:
+    """x[t, c] *= act(gate[t, c]) in place; gate: float32 rows of at least x's width."""
+    gp, gs = _columns(gate, "gate", x.shape[1])
+    if gate.shape[0] != x.shape[0]:
+        raise KernelError("gate_mul: shapes do not fit")
+    _check(_kernels().xrt_gate_mul(_ptr(x, "x"), gp, gs, x.shape[0], x.shape[1], _ACTS[act], _code(x.dtype), _stream()),
+           "gate_mul")
+
+
+def rms_scale_add(residual, y, weight, eps: float, factor: float = 1.0) -> None:
+    """residual += factor * y / sqrt(mean(y^2) + eps) * weight, row by row; all float32."""
+    if residual.shape != y.shape or weight.numel() != y.shape[1]:
+        raise KernelError("rms_scale_add: shapes do not fit")
+    _check(_kernels().xrt_rms_scale_add(_ptr(residual, "residual", torch.float32), _ptr(y, "y", torch.float32),
+                                       _ptr(weight, "weight", torch.float32), y.shape[0], y.shape[1], float(eps),
+                                       float(factor), _stream()), "rms_scale_add")
+
+
+def concat_cast(out, a, b) -> None:
+    """out[t] = [a[t] | b[t]] in out's dtype; a, b float32 [T, width]."""
+    if a.shape != b.shape or out.shape != (a.shape[0], 2 * a.shape[1]):
+        raise KernelError("concat_cast: shapes do not fit")
+    _check(_kernels().xrt_concat_cast(_ptr(out, "out"), _ptr(a, "a", torch.float32), _ptr(b, "b", torch.float32),
+                                     a.shape[0], a.shape[1], _code(out.dtype), _stream()), "concat_cast")
+
+
+def scale_softcap(x, scale: float, cap: float | None) -> None:
+    """x <- cap * tanh(x * scale / cap) in place (x * scale without a cap); x float32 [rows, width]."""
+    _check(_kernels().xrt_scale_softcap(_ptr(x, "x", torch.float32), x.shape[0], x.shape[1], float(scale),
+                                       float(cap) if cap else 0.0, _stream()), "scale_softcap")

@@ -28,6 +28,21 @@ __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __res
   cos_sin[i] = make_float2(c, s);
 }
 
+// cos_sin[t, i] = magnitude * (cos, sin) of pos[t] * freq[i]: a table of frequencies of any make (scaled,
+// blended between two scalings) and one factor on both cos and sin.  The angle is one 32-bit product.
+__global__ void rotation_table_kernel(float2* __restrict__ cos_sin, const int* __restrict__ pos,
+                                      const float* __restrict__ freq, float magnitude, int n_tokens, int half) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * half) return;
+  const int t = i / half, p = i - t * half;
+  const float angle = __fmul_rn((float)pos[t], freq[p]);
+  float s, c;
+  sincosf(angle, &s, &c);
+  cos_sin[i] = make_float2(c * magnitude, s * magnitude);
+}
+
 // One warp per (token, head) among [q heads | k heads | v heads].  MAX_PER_LANE * 32 >= head_dim.
 template <typename TN, typename TQ, typename TC, int MAX_PER_LANE>
 __global__ void qk_rope_kv_write_kernel(
@@ -247,6 +262,16 @@ XRT_EXPORT int xrt_rope_table(float* cos_sin, const int* pos, const float* freq,
   if (total == 0) return XRT_OK;
   xrt::launch_kernel(xrt::rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, (float2*)cos_sin, pos, freq,
                      scale, n_tokens, half);
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_rotation_table(float* cos_sin, const int* pos, const float* freq, float magnitude, int n_tokens,
+                                  int half, cudaStream_t stream) {
+  if (n_tokens < 0 || half < 0) return XRT_ERR_ARGUMENT;
+  const int total = n_tokens * half;
+  if (total == 0) return XRT_OK;
+  xrt::launch_kernel(xrt::rotation_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, (float2*)cos_sin, pos,
+                     freq, magnitude, n_tokens, half);
   return xrt::launch_status();
 }
 

@@ -1,0 +1,419 @@
+// Mixers that keep a matrix state per head instead of keys: the scan over a step's tokens, and the
+// small steps around it.  Everything here is 32-bit: the state, decays, gates of the recurrence,
+// unit norms and head norms.
+//
+//   state scan        S_t = diag(a_t) S_(t-1) + k_t u_t^T,   o_t = S_t^T q_t
+//                     plain:       u_t = v_t                                   (gated linear attention)
+//                     delta rule:  u_t = b_t (v_t - (diag(a_t) S_(t-1))^T k_t) (the read-out sees the write)
+//   short convolution y_t = act(sum_j w[c, j] x_(t - (taps - 1) + j)) per channel, zeros before a sequence's
+//                     start; the last taps - 1 inputs of a sequence are its state
+//   decays            a = sigmoid(z + bias)^(1 / tau)   or   a = exp(-exp(A) softplus(z + bias))
+//   unit heads        x / sqrt(sum(x^2) + eps) * scale per head
+//   head norm + gate  o / sqrt(mean(o^2) + eps) * w * act(g) per head
+//
+// A sequence is a row of the step's cu_seqlens / seq_slot arrays; a row with slot -1 or no tokens is
+// skipped, so padding rows of a captured step leave every state alone.
+#include "common.cuh"
+
+namespace xrt {
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float activate(float z, int act) {  // 0 none, 1 silu, 2 sigmoid
+  return act == 1 ? z * sigmoidf_(z) : (act == 2 ? sigmoidf_(z) : z);
+}
+
+// ------------------------------------------------------------------------------------------ the scan
+// One block: one sequence, one head, COLS value columns.  A column's state S[:, j] (dim rows) is held
+// in registers by PARTS neighbouring lanes, R rows each; sums over rows are finished by a butterfly
+// among those lanes, so every lane of a column holds the same total.  The state is kept column by
+// column, [slot][head][vdim][dim], so that a warp reads and writes it in whole lines.
+// A tile of TT tokens' q, k, a (padded to PARTS * R rows: k = q = 0 there) and the columns' v and b is
+// staged in shared memory; a part's rows start every R + 4 floats so that the parts of a quarter
+// warp read different banks.
+template <int R, bool DELTA>
+__global__ void state_scan_kernel(float* __restrict__ out, const float* __restrict__ q, int q_stride,
+                                  const float* __restrict__ k, int k_stride, const float* __restrict__ v,
+                                  int v_stride, const float* __restrict__ decay, int decay_stride,
+                                  const float* __restrict__ beta, int beta_stride, float* __restrict__ state,
+                                  const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
+                                  int n_heads, int heads_per_qk, int dim, int vdim, float q_scale, int parts,
+                                  int cols, int tile_tokens) {
+  extern __shared__ float tile[];
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int slot = seq_slot[s];
+  const int begin = cu_seqlens[s], end = cu_seqlens[s + 1];
+  if (slot < 0 || end <= begin) return;
+  const int part = threadIdx.x % parts, jl = threadIdx.x / parts;
+  const int j = blockIdx.z * cols + jl;
+  const bool live = j < vdim;
+  const int seg = R + 4, padded = parts * seg;
+  // shared: q | k | a, each [tile_tokens][padded]; then v [tile_tokens][cols]; then b [tile_tokens]
+  float* sq = tile;
+  float* sk = sq + tile_tokens * padded;
+  float* sa = sk + tile_tokens * padded;
+  float* sv = sa + tile_tokens * padded;
+  float* sb = sv + tile_tokens * cols;
+  const int qh = h / heads_per_qk;
+  const int row0 = part * R;
+
+  float S[R];
+  float* sp = state + (((size_t)slot * n_heads + h) * vdim + (live ? j : 0)) * dim + row0;
+#pragma unroll
+  for (int i = 0; i < R; ++i) S[i] = (live && row0 + i < dim) ? sp[i] : 0.f;
+
+  for (int t0 = begin; t0 < end; t0 += tile_tokens) {
+    const int nt = min(tile_tokens, end - t0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nt * parts * R; e += blockDim.x) {
+      const int tt = e / (parts * R), d = e - tt * (parts * R);
+      const int at = tt * padded + (d / R) * seg + (d % R);
+      const size_t t = (size_t)(t0 + tt);
+      const bool in = d < dim;
+      sq[at] = in ? q[t * q_stride + qh * dim + d] * q_scale : 0.f;
+      sk[at] = in ? k[t * k_stride + qh * dim + d] : 0.f;
+      sa[at] = in ? decay[t * decay_stride + h * dim + d] : 1.f;
+    }
+    for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+      const int tt = e / cols, c = e - tt * cols;
+      const int col = blockIdx.z * cols + c;
+      sv[e] = col < vdim ? v[(size_t)(t0 + tt) * v_stride + h * vdim + col] : 0.f;
+    }
+    if (DELTA)
+      for (int tt = threadIdx.x; tt < nt; tt += blockDim.x)
+        sb[tt] = sigmoidf_(beta[(size_t)(t0 + tt) * beta_stride + h]);
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* pq = sq + tt * padded + part * seg;
+      const float* pk = sk + tt * padded + part * seg;
+      const float* pa = sa + tt * padded + part * seg;
+      float u = sv[tt * cols + jl];
+      if (DELTA) {
+        float seen = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          S[i] *= pa[i];
+          seen = fmaf(S[i], pk[i], seen);
+        }
+        for (int o = 1; o < parts; o <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
+        u = sb[tt] * (u - seen);
+      }
+      float read = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        S[i] = DELTA ? fmaf(pk[i], u, S[i]) : fmaf(S[i], pa[i], pk[i] * u);
+        read = fmaf(S[i], pq[i], read);
+      }
+      for (int o = 1; o < parts; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+      if (live && part == 0) out[(size_t)(t0 + tt) * n_heads * vdim + h * vdim + j] = read;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (row0 + i < dim) sp[i] = S[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ convolution
+// grid (sequences, token tiles); threads walk the channels.  Inputs before the step's first token
+// come from the sequence's state [slot][taps - 1][channels] (the newest last).
+__global__ void short_conv_kernel(float* __restrict__ out, const float* __restrict__ x, int x_stride,
+                                  const float* __restrict__ w, const float* __restrict__ state,
+                                  const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int channels,
+                                  int taps, int tile_tokens, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int slot = seq_slot[s];
+  const int begin = cu_seqlens[s], len = cu_seqlens[s + 1] - begin;
+  const int l0 = blockIdx.y * tile_tokens;
+  if (slot < 0 || l0 >= len) return;
+  const int l1 = min(len, l0 + tile_tokens);
+  const float* st = state + (size_t)slot * (taps - 1) * channels;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int l = l0; l < l1; ++l) {
+      float acc = 0.f;
+      for (int jj = 0; jj < taps; ++jj) {
+        const int src = l - (taps - 1) + jj;  // local index of the input under tap jj
+        const float xv = src >= 0 ? x[(size_t)(begin + src) * x_stride + c] : st[(size_t)(taps - 1 + src) * channels + c];
+        acc = fmaf(w[c * taps + jj], xv, acc);
+      }
+      out[(size_t)(begin + l) * channels + c] = activate(acc, act);
+    }
+  }
+}
+
+// The state after the step: the last taps - 1 inputs of the sequence (older ones shift out).
+template <int MAX_KEEP>
+__global__ void short_conv_state_kernel(float* __restrict__ state, const float* __restrict__ x, int x_stride,
+                                        const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
+                                        int channels, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x;
+  const int slot = seq_slot[s];
+  const int begin = cu_seqlens[s], len = cu_seqlens[s + 1] - begin;
+  if (slot < 0 || len <= 0) return;
+  const int keep = taps - 1;
+  float* st = state + (size_t)slot * keep * channels;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+    float next[MAX_KEEP];
+#pragma unroll
+    for (int i = 0; i < MAX_KEEP; ++i) {
+      if (i < keep) {
+        const int src = len - keep + i;
+        next[i] = src >= 0 ? x[(size_t)(begin + src) * x_stride + c] : st[(size_t)(keep + src) * channels + c];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_KEEP; ++i)
+      if (i < keep) st[(size_t)i * channels + c] = next[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ small steps
+// mode 0: a = sigmoid(z + bias)^(1 / tau) = exp(-softplus(-(z + bias)) / tau)
+// mode 1: a = exp(-exp(a_log[head]) * softplus(z + bias))
+__global__ void decay_kernel(float* __restrict__ a, const float* __restrict__ bias, const float* __restrict__ a_log,
+                             size_t total, int width, int dim, int mode, float tau) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % width);
+    const float z = a[i] + (bias != nullptr ? bias[c] : 0.f);
+    a[i] = mode == 0 ? expf(-softplusf_(-z) / tau) : expf(-expf(a_log[c / dim]) * softplusf_(z));
+  }
+}
+
+// One warp a (token, head): x <- x / sqrt(sum(x^2) + eps) * scale, in place; heads [first, first + n).
+__global__ void unit_heads_kernel(float* __restrict__ x, int stride, int n_tokens, int n_heads, int dim, float eps,
+                                  int scaled_heads, float scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_tokens * n_heads) return;
+  const int t = warp / n_heads, head = warp - t * n_heads;
+  float* p = x + (size_t)t * stride + head * dim;
+  float sum = 0.f;
+  for (int d = lane; d < dim; d += 32) sum = fmaf(p[d], p[d], sum);
+  sum = warp_sum(sum);
+  const float f = (head < scaled_heads ? scale : 1.0f) / sqrtf(sum + eps);
+  for (int d = lane; d < dim; d += 32) p[d] *= f;
+}
+
+// One warp a (token, head): y = o / sqrt(mean(o^2) + eps) * w * act(gate).
+template <typename TO>
+__global__ void head_norm_gate_kernel(TO* __restrict__ y, const float* __restrict__ o, const float* __restrict__ w,
+                                      const float* __restrict__ gate, int gate_stride, int n_tokens, int n_heads,
+                                      int vdim, float eps, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_tokens * n_heads) return;
+  const int t = warp / n_heads, head = warp - t * n_heads;
+  const float* p = o + ((size_t)t * n_heads + head) * vdim;
+  const float* g = gate + (size_t)t * gate_stride + head * vdim;
+  float sum = 0.f;
+  for (int d = lane; d < vdim; d += 32) sum = fmaf(p[d], p[d], sum);
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sqrtf(sum / (float)vdim + eps);
+  TO* dst = y + ((size_t)t * n_heads + head) * vdim;
+  for (int d = lane; d < vdim; d += 32) dst[d] = from_float<TO>((p[d] * inv) * w[d] * activate(g[d], act));
+}
+
+// x[t, c] *= act(gate[t, c]) in place.
+template <typename TX>
+__global__ void gate_mul_kernel(TX* __restrict__ x, const float* __restrict__ gate, int gate_stride, int n_tokens,
+                                int width, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)n_tokens * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width, c = i - t * width;
+    x[i] = from_float<TX>(to_float(x[i]) * activate(gate[t * gate_stride + c], act));
+  }
+}
+
+// residual[t] += factor * y[t] / sqrt(mean(y[t]^2) + eps) * w; one block a row.
+__global__ void rms_scale_add_kernel(float* __restrict__ residual, const float* __restrict__ y,
+                                     const float* __restrict__ w, int width, float eps, float factor) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const float* p = y + (size_t)blockIdx.x * width;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) sum = fmaf(p[c], p[c], sum);
+  const float total = block_sum(sum, scratch);
+  const float f = factor / sqrtf(total / (float)width + eps);
+  float* r = residual + (size_t)blockIdx.x * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) r[c] += (p[c] * f) * w[c];
+}
+
+// out[t] = [a[t] | b[t]] in the compute dtype.
+template <typename TO>
+__global__ void concat_cast_kernel(TO* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                   int n_tokens, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)n_tokens * 2 * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / (2 * width), c = i - t * 2 * width;
+    out[i] = from_float<TO>(c < (size_t)width ? a[t * width + c] : b[t * width + c - width]);
+  }
+}
+
+// x <- cap * tanh(x * scale / cap), or x * scale without a cap.
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t total, float scale, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
+}
+
+inline int grid_for(size_t total, int threads) {
+  const size_t blocks = (total + threads - 1) / threads;
+  return (int)(blocks < 148 * 16 ? (blocks ? blocks : 1) : 148 * 16);
+}
+
+}  // namespace xrt
+
+// Rows of a column's state that one lane holds, for a key size: the smallest of 8, 16, 32 that needs
+// at most 32 lanes a column.
+static int scan_rows_per_lane(int dim) { return dim <= 32 ? 8 : (dim <= 128 ? 16 : 32); }
+
+XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const float* k, int k_stride, const float* v,
+                              int v_stride, const float* decay, int decay_stride, const float* beta, int beta_stride,
+                              float* state, const int* cu_seqlens, const int* seq_slot, int n_seqs, int n_heads,
+                              int n_qk_heads, int dim, int vdim, float q_scale, int delta, cudaStream_t stream) {
+  if (n_seqs < 0 || n_heads <= 0 || n_qk_heads <= 0 || n_heads % n_qk_heads || dim <= 0 || vdim <= 0)
+    return XRT_ERR_ARGUMENT;
+  if (dim > 1024 || n_heads > 65535) return XRT_ERR_UNSUPPORTED;
+  if (delta && beta == nullptr) return XRT_ERR_ARGUMENT;
+  if (n_seqs == 0) return XRT_OK;
+  const int R = scan_rows_per_lane(dim);
+  int parts = 1;
+  while (parts * R < dim) parts <<= 1;
+  // 128 threads a block at most, and no more columns than the head has
+  int cols = 128 / parts;
+  while (cols > 1 && cols / 2 >= vdim) cols >>= 1;
+  if (cols > 32) cols = 32;
+  if (parts * cols < 32) cols = 32 / parts;  // whole warps: the butterflies name every lane
+  const int padded = parts * (R + 4);
+  int tile_tokens = 16;
+  while (tile_tokens > 1 && (size_t)tile_tokens * (3 * padded + cols + 1) * sizeof(float) > 40 * 1024) tile_tokens >>= 1;
+  const size_t smem = (size_t)tile_tokens * (3 * padded + cols + 1) * sizeof(float);
+  const dim3 grid(n_seqs, n_heads, (vdim + cols - 1) / cols), block(parts * cols);
+#define XRT_SCAN(RR)                                                                                                  \
+  do {                                                                                                                \
+    if (delta)                                                                                                        \
+      xrt::launch_kernel(xrt::state_scan_kernel<RR, true>, grid, block, smem, stream, out, q, q_stride, k, k_stride, v, \
+                         v_stride, decay, decay_stride, beta, beta_stride, state, cu_seqlens, seq_slot, n_heads,      \
+                         n_heads / n_qk_heads, dim, vdim, q_scale, parts, cols, tile_tokens);                         \
+    else                                                                                                              \
+      xrt::launch_kernel(xrt::state_scan_kernel<RR, false>, grid, block, smem, stream, out, q, q_stride, k, k_stride, v, \
+                         v_stride, decay, decay_stride, beta, beta_stride, state, cu_seqlens, seq_slot, n_heads,      \
+                         n_heads / n_qk_heads, dim, vdim, q_scale, parts, cols, tile_tokens);                         \
+  } while (0)
+  if (R == 8) XRT_SCAN(8);
+  else if (R == 16) XRT_SCAN(16);
+  else XRT_SCAN(32);
+#undef XRT_SCAN
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const float* w, float* state,
+                              const int* cu_seqlens, const int* seq_slot, int n_seqs, int max_new, int channels,
+                              int taps, int act, cudaStream_t stream) {
+  if (n_seqs < 0 || channels <= 0 || taps < 1 || max_new < 0) return XRT_ERR_ARGUMENT;
+  if (taps > 9 || n_seqs > 65535) return XRT_ERR_UNSUPPORTED;
+  if (n_seqs == 0 || max_new == 0) return XRT_OK;
+  const int tile_tokens = 8;
+  const int threads = channels >= 256 ? 256 : (channels >= 128 ? 128 : 64);
+  xrt::launch_kernel(xrt::short_conv_kernel, dim3(n_seqs, (max_new + tile_tokens - 1) / tile_tokens), dim3(threads), 0,
+                     stream, out, x, x_stride, w, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
+                     act);
+  if (taps > 1)
+    xrt::launch_kernel(xrt::short_conv_state_kernel<8>, dim3(n_seqs, (channels + 255) / 256), dim3(256), 0, stream, state,
+                       x, x_stride, cu_seqlens, seq_slot, channels, taps);
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_decay(float* a, const float* bias, const float* a_log, int n_tokens, int n_heads, int dim, int mode,
+                         float tau, cudaStream_t stream) {
+  if (n_tokens < 0 || n_heads <= 0 || dim <= 0 || (mode != 0 && mode != 1)) return XRT_ERR_ARGUMENT;
+  if ((mode == 0 && !(tau > 0.f)) || (mode == 1 && a_log == nullptr)) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  const size_t total = (size_t)n_tokens * n_heads * dim;
+  xrt::launch_kernel(xrt::decay_kernel, dim3(xrt::grid_for(total, 256)), dim3(256), 0, stream, a, bias, a_log, total,
+                     n_heads * dim, dim, mode, tau);
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_unit_heads(float* x, int stride, int n_tokens, int n_heads, int dim, float eps, int scaled_heads,
+                              float scale, cudaStream_t stream) {
+  if (n_tokens < 0 || n_heads <= 0 || dim <= 0 || stride < n_heads * dim) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  const size_t warps = (size_t)n_tokens * n_heads;
+  xrt::launch_kernel(xrt::unit_heads_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, x, stride, n_tokens,
+                     n_heads, dim, eps, scaled_heads, scale);
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_head_norm_gate(void* y, const float* o, const float* w, const float* gate, int gate_stride,
+                                  int n_tokens, int n_heads, int vdim, float eps, int act, int out_dtype,
+                                  cudaStream_t stream) {
+  if (n_tokens < 0 || n_heads <= 0 || vdim <= 0 || gate_stride < n_heads * vdim) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  const size_t warps = (size_t)n_tokens * n_heads;
+  XRT_DISPATCH_DTYPE(out_dtype, TO, {
+    xrt::launch_kernel(xrt::head_norm_gate_kernel<TO>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, (TO*)y, o,
+                       w, gate, gate_stride, n_tokens, n_heads, vdim, eps, act);
+  });
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_gate_mul(void* x, const float* gate, int gate_stride, int n_tokens, int width, int act, int dtype,
+                            cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0 || gate_stride < width) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  XRT_DISPATCH_DTYPE(dtype, TX, {
+    xrt::launch_kernel(xrt::gate_mul_kernel<TX>, dim3(xrt::grid_for((size_t)n_tokens * width, 256)), dim3(256), 0, stream,
+                       (TX*)x, gate, gate_stride, n_tokens, width, act);
+  });
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_rms_scale_add(float* residual, const float* y, const float* w, int n_tokens, int width, float eps,
+                                 float factor, cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+  xrt::launch_kernel(xrt::rms_scale_add_kernel, dim3(n_tokens), dim3(threads), 0, stream, residual, y, w, width, eps,
+                     factor);
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_concat_cast(void* out, const float* a, const float* b, int n_tokens, int width, int out_dtype,
+                               cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  XRT_DISPATCH_DTYPE(out_dtype, TO, {
+    xrt::launch_kernel(xrt::concat_cast_kernel<TO>, dim3(xrt::grid_for((size_t)n_tokens * 2 * width, 256)), dim3(256), 0,
+                       stream, (TO*)out, a, b, n_tokens, width);
+  });
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_scale_softcap(float* x, int n_rows, int width, float scale, float cap, cudaStream_t stream) {
+  if (n_rows < 0 || width <= 0) return XRT_ERR_ARGUMENT;
+  if (n_rows == 0) return XRT_OK;
+  const size_t total = (size_t)n_rows * width;
+  xrt::launch_kernel(xrt::scale_softcap_kernel, dim3(xrt::grid_for(total, 256)), dim3(256), 0, stream, x, total, scale,
+                     cap);
+  return xrt::launch_status();
+}

@@ -16,7 +16,7 @@ from ..core import DType, KernelError, log, parse_dtype, torch_dtype
 from ..csrc import ops
 from ..parts import LayerParts, ModelSpec, part_class
 from ..weights import (INIT_MATRIX_STD, INIT_NORM_STD, load_weights, tensor_key)
-from ..weights.loader import LoadedTensors, kept_dtype
+from ..weights.loader import LoadedTensors, kept_dtype, locate_tensors
 
 
 class Model:
@@ -44,20 +44,21 @@ class Model:
             return cls(part_spec.params, weights, dtype, self.device)
 
         self.embedding = build("embedding", spec.embedding)
+        self.stream_parts = {name: build("stream", part) for name, part in spec.stream_parts.items()}
         self.layers = [LayerParts({name: build(role, part) for name, (role, part) in l.parts.items()},
                                   {name: role for name, (role, _) in l.parts.items()}) for l in spec.layers]
         self.arrangements = [part_class("arrangement", l.arrangement) for l in spec.layers]
         self.final_norm = build("norm", spec.final_norm)
         self.lm_head = build("lm_head", spec.lm_head)
         self.error_flag = ops.device_state(self.device)[0]
-        parts = [self.embedding, self.final_norm, self.lm_head]
+        parts = [self.embedding, self.final_norm, self.lm_head] + list(self.stream_parts.values())
         for layer in self.layers:
             parts += list(layer.values())
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
         # what each place of the schedule is followed by: the first norm of the layer that runs next and
         # the part that takes its result, for arrangements that say so (see parts/block.py)
         firsts = [getattr(fn, "first_norm", None) for fn in self.arrangements]
-        order = [firsts[place.layer](self.layers[place.layer]) if firsts[place.layer] else None
+        order = [firsts[place.layer](self.layers[place.layer]) if firsts[place.layer] and place.before is None else None
                  for place in spec.schedule]
         self._next_layer = order[1:] + [None]
 
@@ -69,6 +70,9 @@ class Model:
         ops.require_device()
         dtype = parse_dtype(dtype)
         arch, config = load_config(folder)
+        if hasattr(config, "with_tensor_shapes"):  # sizes that only the tensors' shapes give
+            header = locate_tensors(folder)[0]
+            config = config.with_tensor_shapes({name: tuple(meta["shape"]) for name, meta in header.items()})
         spec = arch.build_spec(config)
         tensors = load_weights(folder, spec.expected_tensors(), dtype, device, spec.ignorable_tensors,
                                fused_groups=spec.fused_groups())
@@ -146,9 +150,14 @@ class Model:
         logits [len(want_rows), vocab] (None if no row is wanted).  The order inside is that of
         crates/xrt-models/src/llama.rs:432-613; the final norm and the output matrix see only the
         wanted rows (llama.rs:814-819 does so for the last token)."""
-        x = self.embedding.forward(ctx.token_ids, self.error_flag)
+        x = x0 = self.embedding.forward(ctx.token_ids, self.error_flag)
+        if self.stream_parts:
+            x = x0.clone()  # layers change x in place; stream parts read what the embedding gave
         for i, place in enumerate(self.spec.schedule):
             owns = place.cache_from is None
+            if place.before is not None:
+                ctx.pending = ctx.then_norm = None
+                x = self.stream_parts[place.before].forward(x, x0, ctx)
             stores = cache.store(i if owns else place.cache_from) or {}
             ctx.shared["next_layer"] = self._next_layer[i]
             self.arrangements[place.layer](self.layers[place.layer], x, ctx, stores, owns)

@@ -1,5 +1,6 @@
 """Architectures: each module holds a configuration class and the function that turns it into a
 ``ModelSpec``, and registers both under the architecture's name."""
 from . import llama  # registers LlamaForCausalLM and Qwen3ForCausalLM
+from . import givopel  # registers Givopel
 
-__all__ = ["llama"]
+__all__ = ["llama", "givopel"]

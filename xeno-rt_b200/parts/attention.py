@@ -18,57 +18,112 @@ from .linear import linear
 from .registry import part_class, register_part
 
 
+def kernel_head_size(head_dim: int, v_head_dim: int) -> int:
+    """The one head size that the attention kernels and the cache run a layer at: the larger of the key
+    and the value size, rounded up to a multiple of 16."""
+    return -(-max(int(head_dim), int(v_head_dim)) // 16) * 16
+
+
+def _pad_rows(w, heads: int, size: int, to: int):
+    """[heads * size, in] -> [heads * to, in], every head's rows followed by zero rows."""
+    out = torch.zeros((heads, to, w.shape[1]), dtype=w.dtype, device=w.device)
+    out[:, :size] = w.reshape(heads, size, w.shape[1])
+    return out.reshape(heads * to, w.shape[1])
+
+
+def _pad_columns(w, heads: int, size: int, to: int):
+    """[out, heads * size] -> [out, heads * to], every head's columns followed by zero columns."""
+    out = torch.zeros((w.shape[0], heads, to), dtype=w.dtype, device=w.device)
+    out[:, :, :size] = w.reshape(w.shape[0], heads, size)
+    return out.reshape(w.shape[0], heads * to).contiguous()
+
+
 class GroupedQueryAttention:
     """params: ``width`` (model width), ``n_heads``, ``n_kv_heads``, ``head_dim``, ``qk_norm``
     (bool), ``eps`` (of the head norms), ``window`` (None = all keys), ``position`` (a PartSpec-like
-    dict ``{"kind", "params"}``).
-    weights: ``q`` [n_heads*head_dim, width], ``k``, ``v`` [n_kv_heads*head_dim, width],
-    ``o`` [width, n_heads*head_dim], and with qk_norm ``q_norm``, ``k_norm`` [head_dim]."""
+    dict ``{"kind", "params"}``); optional: ``v_head_dim`` (the value size of a head, default
+    head_dim), ``scale`` (of the scores, default 1 / sqrt(head_dim)), ``gate`` ("sigmoid" or "silu":
+    the concatenated heads are multiplied by that function of a product ``g`` of the mixer's input
+    before the output product).
+    weights: ``q`` [n_heads*head_dim, width], ``k`` [n_kv_heads*head_dim, width], ``v``
+    [n_kv_heads*v_head_dim, width], ``o`` [width, n_heads*v_head_dim], with qk_norm ``q_norm``,
+    ``k_norm`` [head_dim], with a gate ``g`` [n_heads*v_head_dim, width].
+
+    The kernels and the cache run a layer at ONE head size.  Where the key and value sizes differ, or
+    are no multiple of 16, every head is laid out at ``kernel_head_size`` with zero rows in q, k, v and
+    g and zero columns in o: zero key dims add nothing to a score, zero value dims come out as zeros
+    and meet zero columns, so the result is that of the true sizes."""
 
     graph_safe = True
 
     @classmethod
+    def _sizes(cls, params):
+        hd = int(params["head_dim"])
+        vd = int(params.get("v_head_dim") or hd)
+        return hd, vd, kernel_head_size(hd, vd)
+
+    @classmethod
     def fused_weights(cls, params):
-        """q, k and v are one matrix [q rows, k rows, v rows] for one product."""
-        return {"qkv": ("q", "k", "v")}
+        """q, k and v (and the gate's matrix) are one matrix [q rows, k rows, v rows, g rows] for one product."""
+        hd, vd, size = cls._sizes(params)
+        if hd != size or vd != size:
+            return {}  # the part lays the heads out itself
+        return {"qkvg": ("q", "k", "v", "g")} if params.get("gate") else {"qkv": ("q", "k", "v")}
 
     @classmethod
     def weight_shapes(cls, params):
-        d, nh, nkv, hd = params["width"], params["n_heads"], params["n_kv_heads"], params["head_dim"]
-        shapes = {"q": ((nh * hd, d), "matrix"), "k": ((nkv * hd, d), "matrix"), "v": ((nkv * hd, d), "matrix"),
-                  "o": ((d, nh * hd), "matrix")}
+        d, nh, nkv = params["width"], params["n_heads"], params["n_kv_heads"]
+        hd, vd, _ = cls._sizes(params)
+        shapes = {"q": ((nh * hd, d), "matrix"), "k": ((nkv * hd, d), "matrix"), "v": ((nkv * vd, d), "matrix"),
+                  "o": ((d, nh * vd), "matrix")}
         if params.get("qk_norm"):
             shapes["q_norm"] = ((hd,), "vector")
             shapes["k_norm"] = ((hd,), "vector")
+        if params.get("gate"):
+            shapes["g"] = ((nh * vd, d), "matrix")
         return shapes
 
     def __init__(self, params, weights, dtype: DType, device):
         self.width = int(params["width"])
         self.n_heads = int(params["n_heads"])
         self.n_kv_heads = int(params["n_kv_heads"])
-        self.head_dim = int(params["head_dim"])
+        true_dim, true_vdim, self.head_dim = self._sizes(params)  # head_dim: the size the kernels and the cache see
         self.eps = float(params.get("eps", 1e-5))
         self.window = params.get("window")
+        self.gate = params.get("gate")
+        if self.gate not in (None, "sigmoid", "silu"):
+            raise ConfigError(f"attention gate {self.gate!r} is not sigmoid or silu")
         if self.n_heads % self.n_kv_heads:
             raise ConfigError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
-        if self.head_dim % 16 or not (16 <= self.head_dim <= 256):
-            raise Unsupported(f"head size {self.head_dim}: the attention kernels take multiples of 16 up to 256")
+        if not (16 <= self.head_dim <= 256):
+            raise Unsupported(f"head size {max(true_dim, true_vdim)}: the attention kernels take head sizes up to 256")
+        if params.get("qk_norm") and true_dim != self.head_dim:
+            raise Unsupported(f"q/k head norms with a head size of {true_dim} (no multiple of 16, or smaller than "
+                              f"the value size) are not supported")
         self.q_width = self.n_heads * self.head_dim
         self.kv_width = self.n_kv_heads * self.head_dim
-        # one fused weight for the three products; the reference fuses only their dispatch (447-486)
-        self.w_qkv = weights.get("qkv")
-        if self.w_qkv is None:  # tensors that came one by one
-            self.w_qkv = torch.cat([weights["q"], weights["k"], weights["v"]], dim=0).contiguous()
-        self.w_q = self.w_qkv[: self.q_width]
+        # one fused weight for the products that read the mixer's input; the reference fuses only their dispatch (447-486)
+        self.w_qkv = weights.get("qkvg" if self.gate else "qkv")
         self.w_o = weights["o"]
+        if self.w_qkv is None:  # tensors that came one by one, or heads that are laid out at another size
+            pieces = [_pad_rows(weights["q"], self.n_heads, true_dim, self.head_dim),
+                      _pad_rows(weights["k"], self.n_kv_heads, true_dim, self.head_dim),
+                      _pad_rows(weights["v"], self.n_kv_heads, true_vdim, self.head_dim)]
+            if self.gate:
+                pieces.append(_pad_rows(weights["g"], self.n_heads, true_vdim, self.head_dim))
+            self.w_qkv = torch.cat(pieces, dim=0).contiguous()
+            if true_vdim != self.head_dim:
+                self.w_o = _pad_columns(weights["o"], self.n_heads, true_vdim, self.head_dim)
+        self.w_q = self.w_qkv[: self.q_width]
+        self.gate_offset = self.q_width + 2 * self.kv_width
         self.q_norm = weights.get("q_norm") if params.get("qk_norm") else None
         self.k_norm = weights.get("k_norm") if params.get("qk_norm") else None
         position = params.get("position") or {"kind": "none", "params": {}}
         self.position = part_class("position", position["kind"])(position.get("params", {}), {}, dtype, device)
         rope_dim = getattr(self.position, "rope_dim", 0)
-        if rope_dim > self.head_dim:
-            raise ConfigError(f"rope_dim {rope_dim} exceeds the head size {self.head_dim}")
-        self.scale = 1.0 / math.sqrt(self.head_dim)
+        if rope_dim > true_dim:
+            raise ConfigError(f"rope_dim {rope_dim} exceeds the head size {true_dim}")
+        self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0 / math.sqrt(true_dim)
         self.dtype = dtype
         self.act_dtype = torch_dtype(dtype)
 
@@ -83,11 +138,25 @@ class GroupedQueryAttention:
         return linear_bf16.takes_pending(rows, self.w_qkv.shape[0], self.width, "store", device)
 
     def forward(self, h, residual, ctx, store, owns_cache=True):
-        n = h.shape[0]
         then_norm = getattr(ctx, "then_norm", None)  # for this part's last product only
         if then_norm is not None:
             ctx.then_norm = None
-        qkv = linear(h, self.w_qkv if owns_cache else self.w_q, out_dtype=torch.float32)
+        attended = self.attended(h, ctx, store, owns_cache)
+        if then_norm is not None:
+            _, ctx.pending = linear(attended, self.w_o, accumulate_into=residual, then_norm=then_norm)
+        else:
+            linear(attended, self.w_o, accumulate_into=residual)
+
+    def mix(self, h, ctx, store, owns_cache=True):
+        """The mixer's result, float32 [T, width], for a caller that does something else with it than adding it."""
+        ctx.then_norm = None
+        return linear(self.attended(h, ctx, store, owns_cache), self.w_o, out_dtype=torch.float32)
+
+    def attended(self, h, ctx, store, owns_cache=True):
+        """The concatenated heads (gated if the layer has a gate) in the compute dtype, [T, heads * head size]."""
+        n = h.shape[0]
+        gated = self.gate is not None
+        qkv = projected = linear(h, self.w_qkv if owns_cache or gated else self.w_q, out_dtype=torch.float32)
         window = int(self.window) if self.window else 0
         pairing = getattr(self.position, "pairing", "split_half")
         cos_sin = self.position.tables(ctx)
@@ -106,10 +175,9 @@ class GroupedQueryAttention:
                                  self.k_norm, self.eps, cos_sin, ctx.tok_slot, ctx.tok_pos, store.block_table,
                                  self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache, pairing=pairing)
             self.attend(attended, q, ctx, store)
-        if then_norm is not None:
-            _, ctx.pending = linear(attended, self.w_o, accumulate_into=residual, then_norm=then_norm)
-        else:
-            linear(attended, self.w_o, accumulate_into=residual)
+        if gated:
+            ops.gate_mul(attended, projected[:, self.gate_offset:], self.gate)
+        return attended
 
     def attend(self, out, q, ctx, store):
         window = int(self.window) if self.window else 0

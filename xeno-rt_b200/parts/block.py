@@ -58,6 +58,21 @@ def _norm_that_can_wait(norm, consumer, ctx, x):
     return norm if can is not None and can(ctx.n_tokens, x.device) else None
 
 
+def parallel_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> None:
+    """x += mixer(norm(x)) + feed_forward(norm(x)): ONE norm whose result both read.  The layer's parts are
+    ``norm``, ``mixer`` and, if it has one, ``ffn``.  Each adds its result into the 32-bit stream."""
+    ctx.then_norm = ctx.pending = None
+    h = parts.norm.forward(x)
+    parts.mixer.forward(h, x, ctx, stores.get("mixer"), owns_cache)
+    ctx.then_norm = ctx.pending = None
+    if "ffn" in parts:
+        parts.ffn.forward(h, x, ctx)
+        ctx.then_norm = ctx.pending = None
+
+
+register_part("arrangement", "parallel_residual", parallel_residual)
+
+
 # what a layer of this arrangement begins with: the norm it applies to the residual stream first, and the
 # part that takes that norm's result
 prenorm_residual.first_norm = lambda parts: (parts.mixer_norm, parts.mixer)

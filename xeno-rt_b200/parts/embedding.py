@@ -32,7 +32,9 @@ class TokenEmbedding:
 class OutputHead:
     """logits = W . normed, no scaling or cap (crates/xrt-models/src/llama.rs:604-613); W is the
     embedding when the model ties them (llama.rs:301-305), which the spec expresses by giving both
-    parts the same tensor name.  params: ``vocab_size``, ``width``.  weights: ``weight``."""
+    parts the same tensor name.  params: ``vocab_size``, ``width``; optional ``scale`` (the logits are
+    multiplied by it) and ``softcap`` (then logits <- softcap * tanh(logits / softcap)), both 32-bit.
+    weights: ``weight``."""
 
     graph_safe = True
 
@@ -42,9 +44,14 @@ class OutputHead:
 
     def __init__(self, params, weights, dtype, device):
         self.weight = weights["weight"]
+        self.scale = float(params.get("scale") or 1.0)
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
 
     def forward(self, normed):
-        return linear(normed, self.weight, out_dtype=torch.float32)
+        logits = linear(normed, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0 or self.softcap is not None:
+            ops.scale_softcap(logits, self.scale, self.softcap)
+        return logits
 
 
 register_part("embedding", "token", TokenEmbedding)

@@ -1,5 +1,5 @@
 """RMSNorm: y = (x / sqrt(mean(x^2) + eps)) * w, statistics in 32-bit
-(crates/xrt-kernels/src/cpu/rmsnorm.rs:26-43)."""
+(crates/xrt-kernels/src/cpu/rmsnorm.rs:26-43), and a layer norm with a weight and no bias."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -60,4 +60,28 @@ class RMSNorm:
         return out
 
 
+class LayerNorm:
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w, no bias, statistics in 32-bit.
+    params: ``width``, ``eps``.  weights: ``weight`` [width]."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {"weight": ((params["width"],), "vector")}
+
+    def __init__(self, params, weights, dtype, device):
+        self.width = int(params["width"])
+        self.eps = float(params["eps"])
+        self.weight = weights["weight"]
+        self.out_dtype = torch_dtype(dtype)
+
+    def forward(self, x, rows=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.width), dtype=self.out_dtype, device=x.device)
+        ops.layernorm(out, x, self.weight, self.eps, rows)
+        return out
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

@@ -17,6 +17,10 @@ position        ``tables(ctx) -> tensor | None``: per-step rotation table [T, ha
                 (cos, sin), cached in ``ctx.shared``; None means no rotation.
 embedding       ``forward(token_ids, error_flag) -> x`` float32 [T, D].
 lm_head         ``forward(normed) -> logits`` float32 [R, V].
+stream          ``forward(x, x0, ctx) -> x``: a step on the residual stream between layers; ``x0`` is what
+                the embedding gave.  It may return a new tensor.  A ``SchedulePlace`` names it in ``before``.
+A mixer may also have ``mix(h, ctx, store, owns_cache) -> float32 [T, D]``: its result handed back instead
+of added, for a mixer that is made of other mixers.
 A part class may set ``graph_safe = True`` to say that its ``forward`` only launches device work
 in stream order whose shapes depend on nothing but the number of tokens and the context bucket (no
 reads back to the host, no data-dependent Python branches); decode steps of a model whose parts
@@ -32,7 +36,7 @@ from __future__ import annotations
 
 from ..core import ConfigError
 
-ROLES = ("norm", "mixer", "feed_forward", "position", "embedding", "lm_head", "arrangement")
+ROLES = ("norm", "mixer", "feed_forward", "position", "embedding", "lm_head", "arrangement", "stream")
 _REGISTRY: dict[str, dict[str, object]] = {role: {} for role in ROLES}
 
 

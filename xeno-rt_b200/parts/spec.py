@@ -46,9 +46,11 @@ def prenorm_layer(mixer_norm: PartSpec, mixer: PartSpec, ffn_norm: PartSpec, ffn
 class SchedulePlace:
     """One place in the order of execution: run ``layer``; ``cache_from`` = None means the place
     owns cache storage of its own, a number means it reads (and does not write) the storage that
-    the earlier place of that index owns."""
+    the earlier place of that index owns.  ``before`` names one of the model's ``stream_parts`` that
+    runs on the residual stream right before this place's layer."""
     layer: int
     cache_from: int | None = None
+    before: str | None = None
 
 
 @dataclass
@@ -63,10 +65,13 @@ class ModelSpec:
     lm_head: PartSpec
     stop_ids: tuple = ()
     ignorable_tensors: tuple = ()
+    stream_parts: dict = field(default_factory=dict)  # {name: PartSpec} of role "stream", run where a place says so
 
     def part_specs(self):
         """Every (role, spec) of the model, each weight-bearing part once."""
         yield "embedding", self.embedding
+        for part in self.stream_parts.values():
+            yield "stream", part
         for layer in self.layers:
             for role, part in layer.parts.values():
                 yield role, part
@@ -111,6 +116,9 @@ class ModelSpec:
         for i, place in enumerate(self.schedule):
             if not (0 <= place.layer < len(self.layers)):
                 raise ConfigError(f"schedule place {i} names layer {place.layer}, the model has {len(self.layers)}")
+            if place.before is not None and place.before not in self.stream_parts:
+                raise ConfigError(f"schedule place {i} names the stream part {place.before!r}, the model has "
+                                  f"{sorted(self.stream_parts)}")
             if place.cache_from is not None:
                 if not (0 <= place.cache_from < i):
                     raise ConfigError(f"schedule place {i} reads the cache of place {place.cache_from}, "

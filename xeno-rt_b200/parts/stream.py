@@ -1,0 +1,34 @@
+"""Steps on the residual stream between layers (role ``stream``)."""
+from __future__ import annotations
+
+import torch
+
+from ..core import torch_dtype
+from ..csrc import ops
+from .linear import linear
+from .registry import register_part
+
+
+class MixWithEmbedding:
+    """x <- W [x; x0]: the stream and what the embedding gave, side by side, through one matrix.  A model that
+    runs a stretch of layers several times begins each pass with it.
+    params: ``width``.  weights: ``weight`` [width, 2 * width], the stream's columns first."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {"weight": ((params["width"], 2 * params["width"]), "matrix")}
+
+    def __init__(self, params, weights, dtype, device):
+        self.width = int(params["width"])
+        self.weight = weights["weight"]
+        self.act_dtype = torch_dtype(dtype)
+
+    def forward(self, x, x0, ctx):
+        both = torch.empty((x.shape[0], 2 * self.width), dtype=self.act_dtype, device=x.device)
+        ops.concat_cast(both, x, x0)
+        return linear(both, self.weight, out_dtype=torch.float32)
+
+
+register_part("stream", "mix_with_embedding", MixWithEmbedding)
