@@ -113,6 +113,20 @@ def short_convolution(x, taps_weight):
     return y
 
 
+def state_scan(q, k, v, decay, beta=None):
+    """One head, token by token: S <- decay_t * S (rows); u = v_t, or with ``beta`` the delta rule
+    u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t.  q, k, decay [T, dim], v [T, vdim], beta [T]."""
+    T, dim = q.shape
+    S = np.zeros((dim, v.shape[1]), F64)
+    out = np.zeros((T, v.shape[1]), F64)
+    for t in range(T):
+        S = decay[t][:, None] * S
+        u = v[t] if beta is None else beta[t] * (v[t] - S.T @ k[t])
+        S = S + np.outer(k[t], u)
+        out[t] = S.T @ q[t]
+    return out
+
+
 def gated_delta_rule(p: dict, w, prefix: str, h, eps: float):
     """The right half: a matrix state per head, decayed per key channel, corrected by the delta rule."""
     T = h.shape[0]
@@ -128,12 +142,7 @@ def gated_delta_rule(p: dict, w, prefix: str, h, eps: float):
     out = np.zeros((T, H, vdim), F64)
     for head in range(H):
         g = head // (H // G)
-        S = np.zeros((dim, vdim), F64)
-        for t in range(T):
-            S = decay[t, head][:, None] * S
-            u = beta[t, head] * (v[t, head] - S.T @ k[t, g])
-            S = S + np.outer(k[t, g], u)
-            out[t, head] = S.T @ q[t, g]
+        out[:, head] = state_scan(q[:, g], k[:, g], v[:, head], decay[:, head], beta[:, head])
     out = out / np.sqrt((out * out).mean(-1, keepdims=True) + eps) * w[prefix + "norm"]
     gate = sigmoid((h @ w[prefix + "g1"].T) @ w[prefix + "g2"].T)
     return (out.reshape(T, H * vdim) * gate) @ w[prefix + "o"].T
@@ -150,10 +159,7 @@ def gated_linear_attention(p: dict, w, prefix: str, h, eps: float):
     alpha = (sigmoid(z) ** (1.0 / p["tau"])).reshape(T, H, dim)
     out = np.zeros((T, H, vdim), F64)
     for head in range(H):
-        S = np.zeros((dim, vdim), F64)
-        for t in range(T):
-            S = alpha[t, head][:, None] * S + np.outer(k[t, head], v[t, head])
-            out[t, head] = S.T @ q[t, head]
+        out[:, head] = state_scan(q[:, head], k[:, head], v[:, head], alpha[:, head])
     out = rms_norm(out, w[prefix + "norm"], eps)
     return (out.reshape(T, H * vdim) * silu(h @ w[prefix + "g"].T)) @ w[prefix + "o"].T
 
