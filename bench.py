@@ -300,6 +300,71 @@ def run_workload(args) -> int:
     return 0
 
 
+def givopel_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: int, layers: int, vocab: int) -> dict:
+    """A Givopel model at the sizes of a dense decoder of that width: layers alternate between the side-by-side
+    mixer (attention of ``heads`` x ``head_dim`` with ``kv_heads`` kv heads; a delta rule of ``heads`` heads with
+    keys and values of ``head_dim``, half as many q/k heads, 4 taps) and gated linear attention (``heads`` / 2
+    heads, keys of ``head_dim``, values of twice that), every layer with a feed-forward of ``inner``; the whole
+    stack is one loop that runs once (so that the step which begins a pass is in the timing)."""
+    rot = {"base": 1000000.0, "dims": head_dim, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    parallel = {"type": "parallel", "mlp": {"kind": "dense", "ff": inner}, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "rot": rot},
+        "right": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": head_dim, "vdim": head_dim, "conv": 4,
+                  "decay_rank": 64, "gate_rank": 64}}}
+    gla = {"type": "gla", "mlp": {"kind": "dense", "ff": inner},
+           "mixer": {"heads": max(1, heads // 2), "dim": head_dim, "vdim": 2 * head_dim, "tau": 16.0, "decay_rank": 64}}
+    return {"architecture": "Givopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "logit_softcap": 30.0, "loop": {"start": 0, "stop": layers, "times": 1},
+            "layers": [parallel if i % 2 == 0 else gla for i in range(layers)]}
+
+
+DESIGN_SIZES = {
+    # name: (width, heads, kv heads, head size, feed-forward width, vocabulary)
+    "2k": (2048, 16, 4, 128, 8192, 32000),
+    "4k": (4096, 32, 8, 128, 14336, 128256),
+}
+
+
+def run_design(args) -> int:
+    """--design givopel: prompt and decode throughput of the Givopel design at sizes that resemble a real model's
+    layers (random weights), beside the dense Llama decoder at the same width, heads, feed-forward width, layers
+    and vocabulary.  One JSON line; every number device-timed as in the headline run."""
+    import torch
+    import xeno_rt_b200  # noqa: F401
+    from xeno_rt_b200.engine import Model
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: bench.py needs a B200"}))
+        return 1
+    if apply_tuning(args):
+        return 2
+    layers = args.layers or 8
+    out = {"design": "givopel", "layers": layers, "prefill_tokens": args.prefill_tokens, "decode_batch": args.batch,
+           "decode_context": args.context, "sizes": {}}
+    for name in (args.design_sizes.split(",") if args.design_sizes else sorted(DESIGN_SIZES)):
+        width, heads, kv_heads, head_dim, inner, vocab = DESIGN_SIZES[name]
+        dense = dict(LLAMA3_8B, vocab_size=vocab, hidden_size=width, intermediate_size=inner, num_hidden_layers=layers,
+                     num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
+                     max_position_embeddings=max(8192, args.context, args.prefill_tokens))
+        row = {}
+        for label, cfg in (("givopel", givopel_config(width, heads, kv_heads, head_dim, inner, layers, vocab)),
+                           ("llama", dense)):
+            model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            prefill_ms = time_prefill(model, args.prefill_tokens, iters=5, warmup=3)
+            decode = time_decode(model, args.batch, args.context, args.steps, max(3, args.warmup))
+            single = time_decode(model, 1, args.context, args.steps, max(3, args.warmup))
+            row[label] = {"prefill_tokens_per_s": round(args.prefill_tokens / (prefill_ms / 1e3), 1),
+                          "prefill_ms": round(prefill_ms, 3),
+                          "decode_tokens_per_s": round(decode["tokens_per_s"], 1),
+                          "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_launches": decode["launches"] // args.steps,
+                          "decode_b1_ms_per_step": round(single["ms_per_step"], 4)}
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args) -> int:
     import torch
     import xeno_rt_b200  # noqa: F401
@@ -480,6 +545,11 @@ def main() -> int:
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
                         help="a short run of one part, for profiling; prints its own small JSON line "
                              "(attention: the decode attention kernel alone)")
+    parser.add_argument("--design", default="", choices=["", "givopel"],
+                        help="instead of the headline line: prompt and decode throughput of that design at sizes that "
+                             "resemble a real model's layers, beside the dense decoder at equal sizes (--layers, default 8; "
+                             "--prefill-tokens, --batch, --context, --steps as for the headline run)")
+    parser.add_argument("--design-sizes", default="", help="--design: which sizes, with commas (default: all of 2k, 4k)")
     parser.add_argument("--window", type=int, default=0, help="--only attention: keys a token sees (0 = all)")
     parser.add_argument("--splits-from", default="window", choices=["window", "context"],
                         help="--only attention with a window: cut the splits from the window's span (what the engine "
@@ -497,6 +567,8 @@ def main() -> int:
         args.warmup = 3
     if args.only == "attention":
         return run_attention_only(args)
+    if args.design:
+        return run_design(args)
     if args.workload:
         apply_tuning(args)
         return run_workload(args)

@@ -108,6 +108,63 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
 
 // Layer norm with a weight and no bias: y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, any width.
 // Two sums over the row in a fixed order (the mean first, then the squared deviations from it).
+// width is a multiple of 4 and at most CHUNKS * NORM_THREADS * 4: the row stays in registers, read once with
+// 16-byte loads that are all in flight together (as rmsnorm_vec_kernel does)
+template <typename TW, typename TO, int CHUNKS>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
+                     const int* __restrict__ rows, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  float wv[CHUNKS][4];
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+    if (c < width) Vec4Of<TW>::load(w + c, wv[i]);
+  }
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows != nullptr ? rows[r] : r;
+  const float* xr = x + (size_t)src * width;
+  float v[CHUNKS][4];
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+    if (c < width) Vec4Of<float>::load(xr + c, v[i]);
+    else v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc += v[i][j];
+  const float mean = block_sum(acc, scratch) / (float)width;
+  acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+    if (c < width) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[i][j] -= mean;
+        acc = fmaf(v[i][j], v[i][j], acc);
+      }
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  TO* dst = out + (size_t)r * width;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (threadIdx.x + i * NORM_THREADS) * 4;
+    if (c < width) {
+      float y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y[j] = (v[i][j] * inv) * wv[i][j];
+      store4(dst + c, y);
+    }
+  }
+}
+
 template <typename TW, typename TO>
 __global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const TW* __restrict__ w,
                                  const int* __restrict__ rows, int width, float eps) {
@@ -139,9 +196,20 @@ XRT_EXPORT int xrt_layernorm(void* out, const float* x, const void* weight, cons
   if (n_rows < 0 || width <= 0) return XRT_ERR_ARGUMENT;
   if (n_rows == 0) return XRT_OK;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+  const bool vec = width % 4 == 0 && (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+  const int chunks = (width / 4 + xrt::NORM_THREADS - 1) / xrt::NORM_THREADS;
   XRT_DISPATCH_DTYPE(weight_dtype, TW, {
     XRT_DISPATCH_DTYPE(out_dtype, TO, {
-      xrt::launch_kernel(xrt::layernorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
+      if (vec && chunks <= 1)
+        xrt::launch_kernel(xrt::layernorm_vec_kernel<TW, TO, 1>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
+      else if (vec && chunks <= 2)
+        xrt::launch_kernel(xrt::layernorm_vec_kernel<TW, TO, 2>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
+      else if (vec && chunks <= 4)
+        xrt::launch_kernel(xrt::layernorm_vec_kernel<TW, TO, 4>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
+      else if (vec && chunks <= 8)
+        xrt::launch_kernel(xrt::layernorm_vec_kernel<TW, TO, 8>, dim3(n_rows), dim3(xrt::NORM_THREADS), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
+      else
+        xrt::launch_kernel(xrt::layernorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, (TO*)out, x, (const TW*)weight, rows, width, eps);
     });
   });
   return xrt::launch_status();

@@ -28,97 +28,173 @@ __device__ __forceinline__ float activate(float z, int act) {  // 0 none, 1 silu
 // in registers by PARTS neighbouring lanes, R rows each; sums over rows are finished by a butterfly
 // among those lanes, so every lane of a column holds the same total.  The state is kept column by
 // column, [slot][head][vdim][dim], so that a warp reads and writes it in whole lines.
-// A tile of TT tokens' q, k, a (padded to PARTS * R rows: k = q = 0 there) and the columns' v and b is
-// staged in shared memory; a part's rows start every R + 4 floats so that the parts of a quarter
-// warp read different banks.
-template <int R, bool DELTA>
-__global__ void state_scan_kernel(float* __restrict__ out, const float* __restrict__ q, int q_stride,
-                                  const float* __restrict__ k, int k_stride, const float* __restrict__ v,
-                                  int v_stride, const float* __restrict__ decay, int decay_stride,
-                                  const float* __restrict__ beta, int beta_stride, float* __restrict__ state,
-                                  const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                                  int n_heads, int heads_per_qk, int dim, int vdim, float q_scale, int parts,
-                                  int cols, int tile_tokens) {
-  extern __shared__ float tile[];
+// Tiles of TT tokens' q, k, a (padded to PARTS * R rows: k = q = 0 there) and the columns' v and b are
+// staged in shared memory by cp.async, two tiles in flight: the next tile lands while this one is
+// worked on.  A part's rows start every R + 4 floats so that the parts of a quarter warp read
+// different banks with 16-byte loads.  Sums over a lane's rows run as four chains.
+template <int BYTES>
+__device__ __forceinline__ void cp_async(float* smem, const float* global) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  if (BYTES == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(global) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(global) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+struct ScanArgs {
+  float* out;
+  const float *q, *k, *v, *decay, *beta;
+  int q_stride, k_stride, v_stride, decay_stride, beta_stride;
+  float* state;
+  const int *cu_seqlens, *seq_slot;
+  int n_heads, heads_per_qk, dim, vdim;
+  float q_scale;
+  int parts, cols, tile_tokens, stage_floats;
+};
+
+// VEC: 16-byte copies (dim, vdim, cols and every row stride are multiples of 4 floats, every base 16-byte aligned)
+template <int R, bool DELTA, bool VEC>
+__global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
+  extern __shared__ float4 tile4[];
+  float* tile = reinterpret_cast<float*>(tile4);
   pdl_trigger();
+  const int parts = a.parts, cols = a.cols, TT = a.tile_tokens, dim = a.dim, vdim = a.vdim;
+  const int seg = R + 4, padded = parts * seg;
+  // a stage: q | k | a, each [TT][padded]; then v [TT][cols]; then b [TT] (regions of whole 16 bytes)
+  const int vec_floats = TT * padded, v_floats = (TT * cols + 3) & ~3;
+  for (int e = threadIdx.x; e < 2 * a.stage_floats; e += blockDim.x) tile[e] = 0.f;  // padding rows and columns stay zero
   pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y;
-  const int slot = seq_slot[s];
-  const int begin = cu_seqlens[s], end = cu_seqlens[s + 1];
+  const int slot = a.seq_slot[s];
+  const int begin = a.cu_seqlens[s], end = a.cu_seqlens[s + 1];
   if (slot < 0 || end <= begin) return;
   const int part = threadIdx.x % parts, jl = threadIdx.x / parts;
-  const int j = blockIdx.z * cols + jl;
+  const int col0 = blockIdx.z * cols;
+  const int j = col0 + jl;
   const bool live = j < vdim;
-  const int seg = R + 4, padded = parts * seg;
-  // shared: q | k | a, each [tile_tokens][padded]; then v [tile_tokens][cols]; then b [tile_tokens]
-  float* sq = tile;
-  float* sk = sq + tile_tokens * padded;
-  float* sa = sk + tile_tokens * padded;
-  float* sv = sa + tile_tokens * padded;
-  float* sb = sv + tile_tokens * cols;
-  const int qh = h / heads_per_qk;
+  const int qh = h / a.heads_per_qk;
   const int row0 = part * R;
+  constexpr int B = VEC ? 16 : 4, E = VEC ? 4 : 1;  // bytes and floats a copy
 
-  float S[R];
-  float* sp = state + (((size_t)slot * n_heads + h) * vdim + (live ? j : 0)) * dim + row0;
-#pragma unroll
-  for (int i = 0; i < R; ++i) S[i] = (live && row0 + i < dim) ? sp[i] : 0.f;
-
-  for (int t0 = begin; t0 < end; t0 += tile_tokens) {
-    const int nt = min(tile_tokens, end - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nt * parts * R; e += blockDim.x) {
-      const int tt = e / (parts * R), d = e - tt * (parts * R);
+  auto issue = [&](int t0, int stage) {
+    float* sq = tile + stage * a.stage_floats;
+    float* sk = sq + vec_floats;
+    float* sa = sk + vec_floats;
+    float* sv = sa + vec_floats;
+    float* sb = sv + v_floats;
+    const int nt = min(TT, end - t0);
+    const int per = dim / E;
+    for (int e = threadIdx.x; e < nt * per; e += blockDim.x) {
+      const int tt = e / per, d = (e - tt * per) * E;
       const int at = tt * padded + (d / R) * seg + (d % R);
       const size_t t = (size_t)(t0 + tt);
-      const bool in = d < dim;
-      sq[at] = in ? q[t * q_stride + qh * dim + d] * q_scale : 0.f;
-      sk[at] = in ? k[t * k_stride + qh * dim + d] : 0.f;
-      sa[at] = in ? decay[t * decay_stride + h * dim + d] : 1.f;
+      cp_async<B>(sq + at, a.q + t * a.q_stride + qh * dim + d);
+      cp_async<B>(sk + at, a.k + t * a.k_stride + qh * dim + d);
+      cp_async<B>(sa + at, a.decay + t * a.decay_stride + h * dim + d);
     }
-    for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
-      const int tt = e / cols, c = e - tt * cols;
-      const int col = blockIdx.z * cols + c;
-      sv[e] = col < vdim ? v[(size_t)(t0 + tt) * v_stride + h * vdim + col] : 0.f;
+    const int vper = cols / E;
+    for (int e = threadIdx.x; e < nt * vper; e += blockDim.x) {
+      const int tt = e / vper, c = (e - tt * vper) * E;
+      if (col0 + c < vdim) cp_async<B>(sv + tt * cols + c, a.v + (size_t)(t0 + tt) * a.v_stride + h * vdim + col0 + c);
     }
     if (DELTA)
       for (int tt = threadIdx.x; tt < nt; tt += blockDim.x)
-        sb[tt] = sigmoidf_(beta[(size_t)(t0 + tt) * beta_stride + h]);
-    __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float* pq = sq + tt * padded + part * seg;
-      const float* pk = sk + tt * padded + part * seg;
-      const float* pa = sa + tt * padded + part * seg;
-      float u = sv[tt * cols + jl];
-      if (DELTA) {
-        float seen = 0.f;
+        cp_async<4>(sb + tt, a.beta + (size_t)(t0 + tt) * a.beta_stride + h);
+    cp_async_commit();
+  };
+
+  float S[R];
+  float* sp = a.state + (((size_t)slot * a.n_heads + h) * vdim + (live ? j : 0)) * dim + row0;
+  if (VEC) {
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          S[i] *= pa[i];
-          seen = fmaf(S[i], pk[i], seen);
-        }
-        for (int o = 1; o < parts; o <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
-        u = sb[tt] * (u - seen);
-      }
-      float read = 0.f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        S[i] = DELTA ? fmaf(pk[i], u, S[i]) : fmaf(S[i], pa[i], pk[i] * u);
-        read = fmaf(S[i], pq[i], read);
-      }
-      for (int o = 1; o < parts; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
-      if (live && part == 0) out[(size_t)(t0 + tt) * n_heads * vdim + h * vdim + j] = read;
+    for (int i = 0; i < R; i += 4) {
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live && row0 + i < dim) t = *reinterpret_cast<const float4*>(sp + i);
+      S[i] = t.x; S[i + 1] = t.y; S[i + 2] = t.z; S[i + 3] = t.w;
     }
+  } else {
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = (live && row0 + i < dim) ? sp[i] : 0.f;
+  }
+  __syncthreads();  // the zero fill is done before the first copies land
+  issue(begin, 0);
+  int stage = 0;
+  for (int t0 = begin; t0 < end; t0 += TT, stage ^= 1) {
+    const int nt = min(TT, end - t0);
+    if (t0 + TT < end) {
+      issue(t0 + TT, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const float* sq = tile + stage * a.stage_floats;
+    const float* sk = sq + vec_floats;
+    const float* sa = sk + vec_floats;
+    const float* sv = sa + vec_floats;
+    const float* sb = sv + v_floats;
+    for (int tt = 0; tt < nt; ++tt) {
+      const float4* pq = reinterpret_cast<const float4*>(sq + tt * padded + part * seg);
+      const float4* pk = reinterpret_cast<const float4*>(sk + tt * padded + part * seg);
+      const float4* pa = reinterpret_cast<const float4*>(sa + tt * padded + part * seg);
+      float u = sv[tt * cols + jl];
+      float kr[R];
+#pragma unroll
+      for (int i = 0; i < R; i += 4) {
+        const float4 t = pk[i / 4];
+        kr[i] = t.x; kr[i + 1] = t.y; kr[i + 2] = t.z; kr[i + 3] = t.w;
+      }
+      if (DELTA) {
+        const float b = sigmoidf_(sb[tt]);
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+          const float4 d = pa[i / 4];
+          S[i] *= d.x; S[i + 1] *= d.y; S[i + 2] *= d.z; S[i + 3] *= d.w;
+          c0 = fmaf(S[i], kr[i], c0); c1 = fmaf(S[i + 1], kr[i + 1], c1);
+          c2 = fmaf(S[i + 2], kr[i + 2], c2); c3 = fmaf(S[i + 3], kr[i + 3], c3);
+        }
+        float seen = (c0 + c1) + (c2 + c3);
+        for (int o = 1; o < parts; o <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
+        u = b * (u - seen);
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+          const float4 d = pa[i / 4];
+          S[i] = fmaf(S[i], d.x, kr[i] * u); S[i + 1] = fmaf(S[i + 1], d.y, kr[i + 1] * u);
+          S[i + 2] = fmaf(S[i + 2], d.z, kr[i + 2] * u); S[i + 3] = fmaf(S[i + 3], d.w, kr[i + 3] * u);
+        }
+      }
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; i += 4) {
+        const float4 qq = pq[i / 4];
+        r0 = fmaf(S[i], qq.x, r0); r1 = fmaf(S[i + 1], qq.y, r1);
+        r2 = fmaf(S[i + 2], qq.z, r2); r3 = fmaf(S[i + 3], qq.w, r3);
+      }
+      float read = (r0 + r1) + (r2 + r3);
+      for (int o = 1; o < parts; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+      if (live && part == 0) a.out[(size_t)(t0 + tt) * a.n_heads * vdim + h * vdim + j] = read * a.q_scale;
+    }
+    __syncthreads();  // the stage is read out before the copies of the tile after next overwrite it
   }
   if (live) {
+    if (VEC) {
 #pragma unroll
-    for (int i = 0; i < R; ++i)
-      if (row0 + i < dim) sp[i] = S[i];
+      for (int i = 0; i < R; i += 4)
+        if (row0 + i < dim) *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+        if (row0 + i < dim) sp[i] = S[i];
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------------ convolution
-// grid (sequences, token tiles); threads walk the channels.  Inputs before the step's first token
+// grid (sequences, token tiles, channel blocks); a thread has one channel of a tile's tokens.  Inputs before the step's first token
 // come from the sequence's state [slot][taps - 1][channels] (the newest last).
 __global__ void short_conv_kernel(float* __restrict__ out, const float* __restrict__ x, int x_stride,
                                   const float* __restrict__ w, const float* __restrict__ state,
@@ -133,7 +209,7 @@ __global__ void short_conv_kernel(float* __restrict__ out, const float* __restri
   if (slot < 0 || l0 >= len) return;
   const int l1 = min(len, l0 + tile_tokens);
   const float* st = state + (size_t)slot * (taps - 1) * channels;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < channels; c += gridDim.z * blockDim.x) {
     for (int l = l0; l < l1; ++l) {
       float acc = 0.f;
       for (int jj = 0; jj < taps; ++jj) {
@@ -237,19 +313,40 @@ __global__ void gate_mul_kernel(TX* __restrict__ x, const float* __restrict__ ga
   }
 }
 
-// residual[t] += factor * y[t] / sqrt(mean(y[t]^2) + eps) * w; one block a row.
+// residual[t] += factor * y[t] / sqrt(mean(y[t]^2) + eps) * w; one block a row.  The row, the weight and the
+// residual are all asked for before the sum (a few rows a step: the time is load latency).
+template <int PER>
 __global__ void rms_scale_add_kernel(float* __restrict__ residual, const float* __restrict__ y,
                                      const float* __restrict__ w, int width, float eps, float factor) {
   __shared__ float scratch[33];
   pdl_trigger();
+  float wv[PER], yv[PER], rv[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    wv[i] = c < width ? w[c] : 0.f;
+  }
   pdl_wait();
   const float* p = y + (size_t)blockIdx.x * width;
+  float* r = residual + (size_t)blockIdx.x * width;
   float sum = 0.f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) sum = fmaf(p[c], p[c], sum);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    yv[i] = c < width ? p[c] : 0.f;
+    rv[i] = c < width ? r[c] : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < PER; ++i) sum = fmaf(yv[i], yv[i], sum);
+  for (int c = threadIdx.x + PER * blockDim.x; c < width; c += blockDim.x) sum = fmaf(p[c], p[c], sum);
   const float total = block_sum(sum, scratch);
   const float f = factor / sqrtf(total / (float)width + eps);
-  float* r = residual + (size_t)blockIdx.x * width;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) r[c] += (p[c] * f) * w[c];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < width) r[c] = rv[i] + (yv[i] * f) * wv[i];
+  }
+  for (int c = threadIdx.x + PER * blockDim.x; c < width; c += blockDim.x) r[c] += (p[c] * f) * w[c];
 }
 
 // out[t] = [a[t] | b[t]] in the compute dtype.
@@ -304,24 +401,30 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
   if (cols > 32) cols = 32;
   if (parts * cols < 32) cols = 32 / parts;  // whole warps: the butterflies name every lane
   const int padded = parts * (R + 4);
+  auto stage_floats = [&](int tt) { return 3 * tt * padded + ((tt * cols + 3) & ~3) + ((tt + 3) & ~3); };
   int tile_tokens = 16;
-  while (tile_tokens > 1 && (size_t)tile_tokens * (3 * padded + cols + 1) * sizeof(float) > 40 * 1024) tile_tokens >>= 1;
-  const size_t smem = (size_t)tile_tokens * (3 * padded + cols + 1) * sizeof(float);
+  while (tile_tokens > 1 && 2 * (size_t)stage_floats(tile_tokens) * sizeof(float) > 44 * 1024) tile_tokens >>= 1;
+  const size_t smem = 2 * (size_t)stage_floats(tile_tokens) * sizeof(float);
+  if (smem > 48 * 1024) return XRT_ERR_UNSUPPORTED;
+  const bool vec = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 &&
+                   v_stride % 4 == 0 && decay_stride % 4 == 0 &&
+                   (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay | (uintptr_t)state) & 15) == 0;
+  xrt::ScanArgs a = {out, q, k, v, decay, beta, q_stride, k_stride, v_stride, decay_stride, beta_stride, state,
+                     cu_seqlens, seq_slot, n_heads, n_heads / n_qk_heads, dim, vdim, q_scale, parts, cols, tile_tokens,
+                     stage_floats(tile_tokens)};
   const dim3 grid(n_seqs, n_heads, (vdim + cols - 1) / cols), block(parts * cols);
-#define XRT_SCAN(RR)                                                                                                  \
-  do {                                                                                                                \
-    if (delta)                                                                                                        \
-      xrt::launch_kernel(xrt::state_scan_kernel<RR, true>, grid, block, smem, stream, out, q, q_stride, k, k_stride, v, \
-                         v_stride, decay, decay_stride, beta, beta_stride, state, cu_seqlens, seq_slot, n_heads,      \
-                         n_heads / n_qk_heads, dim, vdim, q_scale, parts, cols, tile_tokens);                         \
-    else                                                                                                              \
-      xrt::launch_kernel(xrt::state_scan_kernel<RR, false>, grid, block, smem, stream, out, q, q_stride, k, k_stride, v, \
-                         v_stride, decay, decay_stride, beta, beta_stride, state, cu_seqlens, seq_slot, n_heads,      \
-                         n_heads / n_qk_heads, dim, vdim, q_scale, parts, cols, tile_tokens);                         \
+#define XRT_SCAN(RR, DD, VV) xrt::launch_kernel(xrt::state_scan_kernel<RR, DD, VV>, grid, block, smem, stream, a)
+#define XRT_SCAN_R(RR)                                     \
+  do {                                                     \
+    if (delta && vec) XRT_SCAN(RR, true, true);            \
+    else if (delta) XRT_SCAN(RR, true, false);             \
+    else if (vec) XRT_SCAN(RR, false, true);               \
+    else XRT_SCAN(RR, false, false);                       \
   } while (0)
-  if (R == 8) XRT_SCAN(8);
-  else if (R == 16) XRT_SCAN(16);
-  else XRT_SCAN(32);
+  if (R == 8) XRT_SCAN_R(8);
+  else if (R == 16) XRT_SCAN_R(16);
+  else XRT_SCAN_R(32);
+#undef XRT_SCAN_R
 #undef XRT_SCAN
   return xrt::launch_status();
 }
@@ -333,9 +436,11 @@ XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const fl
   if (taps > 9 || n_seqs > 65535) return XRT_ERR_UNSUPPORTED;
   if (n_seqs == 0 || max_new == 0) return XRT_OK;
   const int tile_tokens = 8;
-  const int threads = channels >= 256 ? 256 : (channels >= 128 ? 128 : 64);
-  xrt::launch_kernel(xrt::short_conv_kernel, dim3(n_seqs, (max_new + tile_tokens - 1) / tile_tokens), dim3(threads), 0,
-                     stream, out, x, x_stride, w, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
+  const int threads = channels >= 128 ? 128 : 64;
+  const int channel_blocks = (channels + threads - 1) / threads;
+  xrt::launch_kernel(xrt::short_conv_kernel,
+                     dim3(n_seqs, (max_new + tile_tokens - 1) / tile_tokens, channel_blocks < 65535 ? channel_blocks : 65535),
+                     dim3(threads), 0, stream, out, x, x_stride, w, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
                      act);
   if (taps > 1)
     xrt::launch_kernel(xrt::short_conv_state_kernel<8>, dim3(n_seqs, (channels + 255) / 256), dim3(256), 0, stream, state,
@@ -393,8 +498,12 @@ XRT_EXPORT int xrt_rms_scale_add(float* residual, const float* y, const float* w
   if (n_tokens < 0 || width <= 0) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
-  xrt::launch_kernel(xrt::rms_scale_add_kernel, dim3(n_tokens), dim3(threads), 0, stream, residual, y, w, width, eps,
-                     factor);
+  if (width <= 4 * threads)
+    xrt::launch_kernel(xrt::rms_scale_add_kernel<4>, dim3(n_tokens), dim3(threads), 0, stream, residual, y, w, width, eps,
+                       factor);
+  else
+    xrt::launch_kernel(xrt::rms_scale_add_kernel<16>, dim3(n_tokens), dim3(threads), 0, stream, residual, y, w, width,
+                       eps, factor);
   return xrt::launch_status();
 }
 
