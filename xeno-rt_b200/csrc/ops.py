@@ -31,7 +31,7 @@ _SIGNATURES = {
     "xrt_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _P],
     "xrt_rotation_table": [_P, _P, _P, _F, _I, _I, _P],
-    "xrt_state_scan": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "xrt_state_scan": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "xrt_short_conv": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "xrt_decay": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
     "xrt_unit_heads": [_P, _I, _I, _I, _I, _F, _I, _F, _P],
@@ -742,12 +742,13 @@ def rotation_table(cos_sin, positions, freq, magnitude: float = 1.0) -> None:
 
 
 def state_scan(out, q, k, v, decay, beta, state, cu_seqlens, seq_slot, n_heads: int, n_qk_heads: int, dim: int,
-               vdim: int, q_scale: float = 1.0, delta: bool = False) -> None:
+               vdim: int, q_scale: float = 1.0, delta: bool = False, max_new: int = 0) -> None:
     """The scan of a matrix state over the step's tokens, a sequence after the other in parallel:
     S <- diag(decay_t) S + k_t u_t^T and out_t = S^T (q_t * q_scale), with u_t = v_t, or with ``delta``
     u_t = sigmoid(beta_t) (v_t - S^T k_t) taken after the decay.  q, k [T, n_qk_heads * dim], v [T, n_heads * vdim],
     decay [T, n_heads * dim] (rows may be slices of wider rows), beta [T, n_heads] before its sigmoid, all
-    float32; ``state`` float32 [slots, n_heads, vdim, dim] is read and left as the sequences' last state."""
+    float32; ``state`` float32 [slots, n_heads, vdim, dim] is read and left as the sequences' last state.
+    ``max_new`` (0: not known): the most tokens a sequence brings, from which the kernel sizes its tiles."""
     n = out.shape[0]
     if out.shape != (n, n_heads * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
         raise KernelError("state_scan: out must be float32 [T, heads * vdim]")
@@ -766,7 +767,8 @@ def state_scan(out, q, k, v, decay, beta, state, cu_seqlens, seq_slot, n_heads: 
         raise KernelError("state_scan: cu_seqlens must hold one entry more than seq_slot")
     _check(_kernels().xrt_state_scan(_ptr(out, "out"), qp, qs, kp, ks, vp, vs, dp, ds, bp, bs, _ptr(state, "state"),
                                     _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
-                                    n_seqs, n_heads, n_qk_heads, dim, vdim, float(q_scale), 1 if delta else 0, _stream()),
+                                    n_seqs, n_heads, n_qk_heads, dim, vdim, float(q_scale), 1 if delta else 0, int(max_new),
+                                    _stream()),
            "state_scan")
 
 

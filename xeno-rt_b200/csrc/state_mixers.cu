@@ -30,8 +30,9 @@ __device__ __forceinline__ float activate(float z, int act) {  // 0 none, 1 silu
 // column, [slot][head][vdim][dim], so that a warp reads and writes it in whole lines.
 // Tiles of TT tokens' q, k, a (padded to PARTS * R rows: k = q = 0 there) and the columns' v and b are
 // staged in shared memory by cp.async, two tiles in flight: the next tile lands while this one is
-// worked on.  A part's rows start every R + 4 floats so that the parts of a quarter warp read
-// different banks with 16-byte loads.  Sums over a lane's rows run as four chains.
+// worked on.  A lane's rows are every PARTS-th group of four (lane p holds rows 4 (i PARTS + p) .. + 3), so
+// that the lanes of a column read neighbouring 16 bytes at a time: whole lines of the state in global
+// memory, different banks of shared memory.  Sums over a lane's rows run as two chains.
 template <int BYTES>
 __device__ __forceinline__ void cp_async(float* smem, const float* global) {
   const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
@@ -52,29 +53,31 @@ struct ScanArgs {
   int parts, cols, tile_tokens, stage_floats;
 };
 
-// VEC: 16-byte copies (dim, vdim, cols and every row stride are multiples of 4 floats, every base 16-byte aligned)
-template <int R, bool DELTA, bool VEC>
+// VEC: 16-byte copies (dim, vdim, cols and every row stride are multiples of 4 floats, every base 16-byte aligned).
+// C2: value columns a lane holds (C2 * R state registers): what a lane reads of q, k and a serves C2 columns, and
+// the kernel is bound by what its warps ask of shared memory.
+template <int R, int C2, bool DELTA, bool VEC>
 __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
   extern __shared__ float4 tile4[];
   float* tile = reinterpret_cast<float*>(tile4);
   pdl_trigger();
   const int parts = a.parts, cols = a.cols, TT = a.tile_tokens, dim = a.dim, vdim = a.vdim;
-  const int seg = R + 4, padded = parts * seg;
+  const int padded = parts * R;
   // a stage: q | k | a, each [TT][padded]; then v [TT][cols]; then b [TT] (regions of whole 16 bytes)
   const int vec_floats = TT * padded, v_floats = (TT * cols + 3) & ~3;
-  for (int e = threadIdx.x; e < 2 * a.stage_floats; e += blockDim.x) tile[e] = 0.f;  // padding rows and columns stay zero
+  if (padded != dim || vdim % cols != 0)  // rows and columns beyond the head's stay zero
+    for (int e = threadIdx.x; e < 2 * a.stage_floats; e += blockDim.x) tile[e] = 0.f;
   pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y;
   const int slot = a.seq_slot[s];
   const int begin = a.cu_seqlens[s], end = a.cu_seqlens[s + 1];
   if (slot < 0 || end <= begin) return;
-  const int part = threadIdx.x % parts, jl = threadIdx.x / parts;
+  const int part = threadIdx.x % parts, jl = (threadIdx.x / parts) * C2;  // the lane's first column in the block
   const int col0 = blockIdx.z * cols;
   const int j = col0 + jl;
-  const bool live = j < vdim;
   const int qh = h / a.heads_per_qk;
-  const int row0 = part * R;
   constexpr int B = VEC ? 16 : 4, E = VEC ? 4 : 1;  // bytes and floats a copy
+  auto row_of = [&](int i) { return 4 * ((i / 4) * parts + part) + (i & 3); };  // the lane's i-th row
 
   auto issue = [&](int t0, int stage) {
     float* sq = tile + stage * a.stage_floats;
@@ -86,7 +89,7 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
     const int per = dim / E;
     for (int e = threadIdx.x; e < nt * per; e += blockDim.x) {
       const int tt = e / per, d = (e - tt * per) * E;
-      const int at = tt * padded + (d / R) * seg + (d % R);
+      const int at = tt * padded + d;
       const size_t t = (size_t)(t0 + tt);
       cp_async<B>(sq + at, a.q + t * a.q_stride + qh * dim + d);
       cp_async<B>(sk + at, a.k + t * a.k_stride + qh * dim + d);
@@ -103,18 +106,22 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
     cp_async_commit();
   };
 
-  float S[R];
-  float* sp = a.state + (((size_t)slot * a.n_heads + h) * vdim + (live ? j : 0)) * dim + row0;
-  if (VEC) {
+  float S[C2][R];
+  float* sp = a.state + (((size_t)slot * a.n_heads + h) * vdim + j) * dim;  // column j + c is c * dim further
 #pragma unroll
-    for (int i = 0; i < R; i += 4) {
-      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (live && row0 + i < dim) t = *reinterpret_cast<const float4*>(sp + i);
-      S[i] = t.x; S[i + 1] = t.y; S[i + 2] = t.z; S[i + 3] = t.w;
+  for (int c = 0; c < C2; ++c) {
+    const bool live = j + c < vdim;
+    if (VEC) {
+#pragma unroll
+      for (int i = 0; i < R; i += 4) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live && row_of(i) < dim) t = *reinterpret_cast<const float4*>(sp + (size_t)c * dim + row_of(i));
+        S[c][i] = t.x; S[c][i + 1] = t.y; S[c][i + 2] = t.z; S[c][i + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < R; ++i) S[c][i] = (live && row_of(i) < dim) ? sp[(size_t)c * dim + row_of(i)] : 0.f;
     }
-  } else {
-#pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = (live && row0 + i < dim) ? sp[i] : 0.f;
   }
   __syncthreads();  // the zero fill is done before the first copies land
   issue(begin, 0);
@@ -127,68 +134,97 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
     } else {
       cp_async_wait<0>();
     }
-    __syncthreads();
     const float* sq = tile + stage * a.stage_floats;
     const float* sk = sq + vec_floats;
     const float* sa = sk + vec_floats;
     const float* sv = sa + vec_floats;
-    const float* sb = sv + v_floats;
+    float* sb = tile + stage * a.stage_floats + 3 * vec_floats + v_floats;
+    if (DELTA)  // b = sigmoid(raw), once a tile, by the thread whose own copy brought the raw value
+      for (int tt = threadIdx.x; tt < nt; tt += blockDim.x) sb[tt] = sigmoidf_(sb[tt]);
+    __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float4* pq = reinterpret_cast<const float4*>(sq + tt * padded + part * seg);
-      const float4* pk = reinterpret_cast<const float4*>(sk + tt * padded + part * seg);
-      const float4* pa = reinterpret_cast<const float4*>(sa + tt * padded + part * seg);
-      float u = sv[tt * cols + jl];
+      // the lane's i-th group of four rows is 16-byte element i * parts of these
+      const float4* pq = reinterpret_cast<const float4*>(sq + tt * padded) + part;
+      const float4* pk = reinterpret_cast<const float4*>(sk + tt * padded) + part;
+      const float4* pa = reinterpret_cast<const float4*>(sa + tt * padded) + part;
+      float u[C2];
+#pragma unroll
+      for (int c = 0; c < C2; ++c) u[c] = sv[tt * cols + jl + c];
       float kr[R];
 #pragma unroll
       for (int i = 0; i < R; i += 4) {
-        const float4 t = pk[i / 4];
+        const float4 t = pk[(i / 4) * parts];
         kr[i] = t.x; kr[i + 1] = t.y; kr[i + 2] = t.z; kr[i + 3] = t.w;
       }
       if (DELTA) {
-        const float b = sigmoidf_(sb[tt]);
-        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+        const float b = sb[tt];
+        float seen[C2][2];
+#pragma unroll
+        for (int c = 0; c < C2; ++c) seen[c][0] = seen[c][1] = 0.f;
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
-          const float4 d = pa[i / 4];
-          S[i] *= d.x; S[i + 1] *= d.y; S[i + 2] *= d.z; S[i + 3] *= d.w;
-          c0 = fmaf(S[i], kr[i], c0); c1 = fmaf(S[i + 1], kr[i + 1], c1);
-          c2 = fmaf(S[i + 2], kr[i + 2], c2); c3 = fmaf(S[i + 3], kr[i + 3], c3);
-        }
-        float seen = (c0 + c1) + (c2 + c3);
-        for (int o = 1; o < parts; o <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
-        u = b * (u - seen);
+          const float4 d = pa[(i / 4) * parts];
 #pragma unroll
-        for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
+          for (int c = 0; c < C2; ++c) {
+            S[c][i] *= d.x; S[c][i + 1] *= d.y; S[c][i + 2] *= d.z; S[c][i + 3] *= d.w;
+            seen[c][0] = fmaf(S[c][i], kr[i], seen[c][0]); seen[c][1] = fmaf(S[c][i + 1], kr[i + 1], seen[c][1]);
+            seen[c][0] = fmaf(S[c][i + 2], kr[i + 2], seen[c][0]); seen[c][1] = fmaf(S[c][i + 3], kr[i + 3], seen[c][1]);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < C2; ++c) {
+          float total = seen[c][0] + seen[c][1];
+          for (int o = 1; o < parts; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+          u[c] = b * (u[c] - total);
+        }
+#pragma unroll
+        for (int c = 0; c < C2; ++c)
+#pragma unroll
+          for (int i = 0; i < R; ++i) S[c][i] = fmaf(kr[i], u[c], S[c][i]);
       } else {
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
-          const float4 d = pa[i / 4];
-          S[i] = fmaf(S[i], d.x, kr[i] * u); S[i + 1] = fmaf(S[i + 1], d.y, kr[i + 1] * u);
-          S[i + 2] = fmaf(S[i + 2], d.z, kr[i + 2] * u); S[i + 3] = fmaf(S[i + 3], d.w, kr[i + 3] * u);
+          const float4 d = pa[(i / 4) * parts];
+#pragma unroll
+          for (int c = 0; c < C2; ++c) {
+            S[c][i] = fmaf(S[c][i], d.x, kr[i] * u[c]); S[c][i + 1] = fmaf(S[c][i + 1], d.y, kr[i + 1] * u[c]);
+            S[c][i + 2] = fmaf(S[c][i + 2], d.z, kr[i + 2] * u[c]); S[c][i + 3] = fmaf(S[c][i + 3], d.w, kr[i + 3] * u[c]);
+          }
         }
       }
-      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+      float read[C2][2];
+#pragma unroll
+      for (int c = 0; c < C2; ++c) read[c][0] = read[c][1] = 0.f;
 #pragma unroll
       for (int i = 0; i < R; i += 4) {
-        const float4 qq = pq[i / 4];
-        r0 = fmaf(S[i], qq.x, r0); r1 = fmaf(S[i + 1], qq.y, r1);
-        r2 = fmaf(S[i + 2], qq.z, r2); r3 = fmaf(S[i + 3], qq.w, r3);
+        const float4 qq = pq[(i / 4) * parts];
+#pragma unroll
+        for (int c = 0; c < C2; ++c) {
+          read[c][0] = fmaf(S[c][i], qq.x, read[c][0]); read[c][1] = fmaf(S[c][i + 1], qq.y, read[c][1]);
+          read[c][0] = fmaf(S[c][i + 2], qq.z, read[c][0]); read[c][1] = fmaf(S[c][i + 3], qq.w, read[c][1]);
+        }
       }
-      float read = (r0 + r1) + (r2 + r3);
-      for (int o = 1; o < parts; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
-      if (live && part == 0) a.out[(size_t)(t0 + tt) * a.n_heads * vdim + h * vdim + j] = read * a.q_scale;
+#pragma unroll
+      for (int c = 0; c < C2; ++c) {
+        float total = read[c][0] + read[c][1];
+        for (int o = 1; o < parts; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if (part == 0 && j + c < vdim) a.out[(size_t)(t0 + tt) * a.n_heads * vdim + h * vdim + j + c] = total * a.q_scale;
+      }
     }
     __syncthreads();  // the stage is read out before the copies of the tile after next overwrite it
   }
-  if (live) {
+#pragma unroll
+  for (int c = 0; c < C2; ++c) {
+    if (j + c >= vdim) continue;
     if (VEC) {
 #pragma unroll
       for (int i = 0; i < R; i += 4)
-        if (row0 + i < dim) *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        if (row_of(i) < dim)
+          *reinterpret_cast<float4*>(sp + (size_t)c * dim + row_of(i)) = make_float4(S[c][i], S[c][i + 1], S[c][i + 2], S[c][i + 3]);
     } else {
 #pragma unroll
       for (int i = 0; i < R; ++i)
-        if (row0 + i < dim) sp[i] = S[i];
+        if (row_of(i) < dim) sp[(size_t)c * dim + row_of(i)] = S[c][i];
     }
   }
 }
@@ -381,12 +417,14 @@ inline int grid_for(size_t total, int threads) {
 
 // Rows of a column's state that one lane holds, for a key size: the smallest of 8, 16, 32 that needs
 // at most 32 lanes a column.
-static int scan_rows_per_lane(int dim) { return dim <= 32 ? 8 : (dim <= 128 ? 16 : 32); }
+static int scan_rows_per_lane(int dim) { return dim <= 32 ? 8 : (dim <= 64 ? 16 : 32); }
 
 XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const float* k, int k_stride, const float* v,
                               int v_stride, const float* decay, int decay_stride, const float* beta, int beta_stride,
                               float* state, const int* cu_seqlens, const int* seq_slot, int n_seqs, int n_heads,
-                              int n_qk_heads, int dim, int vdim, float q_scale, int delta, cudaStream_t stream) {
+                              int n_qk_heads, int dim, int vdim, float q_scale, int delta, int max_new,
+                              cudaStream_t stream) {
+  if (max_new < 1) max_new = 1 << 30;
   if (n_seqs < 0 || n_heads <= 0 || n_qk_heads <= 0 || n_heads % n_qk_heads || dim <= 0 || vdim <= 0)
     return XRT_ERR_ARGUMENT;
   if (dim > 1024 || n_heads > 65535) return XRT_ERR_UNSUPPORTED;
@@ -395,15 +433,22 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
   const int R = scan_rows_per_lane(dim);
   int parts = 1;
   while (parts * R < dim) parts <<= 1;
-  // 128 threads a block at most, and no more columns than the head has
-  int cols = 128 / parts;
-  while (cols > 1 && cols / 2 >= vdim) cols >>= 1;
-  if (cols > 32) cols = 32;
-  if (parts * cols < 32) cols = 32 / parts;  // whole warps: the butterflies name every lane
-  const int padded = parts * (R + 4);
+  // columns a lane holds: one.  (Several, so that what a lane reads of q, k and a serves more columns, was
+  // measured slower: 1.77 against 0.96 ms for 2,048 tokens of 32 heads of 128 x 128; a token's time is the
+  // chain of dependent instructions of ONE warp, and more columns a lane make that chain longer.)
+  const int per_lane = 1;
+  // 128 threads a block at most, whole warps at least
+  int groups = 128 / parts;
+  if (groups < 1) groups = 1;
+  while (groups > 1 && (groups / 2) * per_lane >= vdim && (groups / 2) * parts >= 32) groups >>= 1;
+  if (groups * parts < 32) groups = 32 / parts;
+  const int cols = groups * per_lane;
+  const int padded = parts * R;
   auto stage_floats = [&](int tt) { return 3 * tt * padded + ((tt * cols + 3) & ~3) + ((tt + 3) & ~3); };
   int tile_tokens = 16;
   while (tile_tokens > 1 && 2 * (size_t)stage_floats(tile_tokens) * sizeof(float) > 44 * 1024) tile_tokens >>= 1;
+  // no more than the step's longest sequence brings: a decode step's blocks are small and many fit a multiprocessor
+  while (tile_tokens > 1 && tile_tokens / 2 >= max_new) tile_tokens >>= 1;
   const size_t smem = 2 * (size_t)stage_floats(tile_tokens) * sizeof(float);
   if (smem > 48 * 1024) return XRT_ERR_UNSUPPORTED;
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 &&
@@ -412,18 +457,24 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
   xrt::ScanArgs a = {out, q, k, v, decay, beta, q_stride, k_stride, v_stride, decay_stride, beta_stride, state,
                      cu_seqlens, seq_slot, n_heads, n_heads / n_qk_heads, dim, vdim, q_scale, parts, cols, tile_tokens,
                      stage_floats(tile_tokens)};
-  const dim3 grid(n_seqs, n_heads, (vdim + cols - 1) / cols), block(parts * cols);
-#define XRT_SCAN(RR, DD, VV) xrt::launch_kernel(xrt::state_scan_kernel<RR, DD, VV>, grid, block, smem, stream, a)
-#define XRT_SCAN_R(RR)                                     \
-  do {                                                     \
-    if (delta && vec) XRT_SCAN(RR, true, true);            \
-    else if (delta) XRT_SCAN(RR, true, false);             \
-    else if (vec) XRT_SCAN(RR, false, true);               \
-    else XRT_SCAN(RR, false, false);                       \
+  const dim3 grid(n_seqs, n_heads, (vdim + cols - 1) / cols), block(parts * groups);
+#define XRT_SCAN(RR, CC, DD, VV) xrt::launch_kernel(xrt::state_scan_kernel<RR, CC, DD, VV>, grid, block, smem, stream, a)
+#define XRT_SCAN_R(RR, CC)                                     \
+  do {                                                         \
+    if (delta && vec) XRT_SCAN(RR, CC, true, true);            \
+    else if (delta) XRT_SCAN(RR, CC, true, false);             \
+    else if (vec) XRT_SCAN(RR, CC, false, true);               \
+    else XRT_SCAN(RR, CC, false, false);                       \
   } while (0)
-  if (R == 8) XRT_SCAN_R(8);
-  else if (R == 16) XRT_SCAN_R(16);
-  else XRT_SCAN_R(32);
+  if (per_lane == 1) {
+    if (R == 8) XRT_SCAN_R(8, 1);
+    else if (R == 16) XRT_SCAN_R(16, 1);
+    else XRT_SCAN_R(32, 1);
+  } else {
+    if (R == 8) XRT_SCAN_R(8, 4);
+    else if (R == 16) XRT_SCAN_R(16, 4);
+    else XRT_SCAN_R(32, 2);
+  }
 #undef XRT_SCAN_R
 #undef XRT_SCAN
   return xrt::launch_status();

@@ -87,7 +87,7 @@ class GatedLinearAttention(_StateMixer):
         ops.decay_from_gate(decay, self.a2_bias, nh, kd, self.tau)
         o = torch.zeros((n, nh * vd), dtype=torch.float32, device=h.device)  # rows of no sequence stay zero
         ops.state_scan(o, p, p[:, nh * kd:], p[:, 2 * nh * kd:], decay, None, store.state, ctx.cu_seqlens, ctx.seq_slot,
-                       nh, nh, kd, vd, q_scale=kd ** -0.5)
+                       nh, nh, kd, vd, q_scale=kd ** -0.5, max_new=ctx.max_new)
         y = torch.empty((n, nh * vd), dtype=self.act_dtype, device=h.device)
         ops.head_norm_gate(y, o, self.norm, p[:, 2 * nh * kd + nh * vd:], nh, vd, self.eps, "silu")
         return y
@@ -164,7 +164,7 @@ class GatedDeltaRule(_StateMixer):
         ops.unit_heads(qkv, 2 * nq, kd, self.UNIT_EPS, scaled_heads=nq, scale=kd ** -0.5)
         o = torch.zeros((n, nh * vd), dtype=torch.float32, device=h.device)
         ops.state_scan(o, qkv, qkv[:, nq * kd:], qkv[:, 2 * nq * kd:], decay, p[:, self.channels:], store[0].state,
-                       ctx.cu_seqlens, ctx.seq_slot, nh, nq, kd, vd, delta=True)
+                       ctx.cu_seqlens, ctx.seq_slot, nh, nq, kd, vd, delta=True, max_new=ctx.max_new)
         y = torch.empty((n, nh * vd), dtype=self.act_dtype, device=h.device)
         ops.head_norm_gate(y, o, self.norm, gate, nh, vd, self.eps, "sigmoid")
         return y
