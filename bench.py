@@ -338,6 +338,21 @@ def run_design(args) -> int:
         return 1
     if apply_tuning(args):
         return 2
+    if args.only in ("prefill", "decode"):  # a short run for profiling: the design's model alone, one part
+        name = (args.design_sizes or "4k").split(",")[0]
+        width, heads, kv_heads, head_dim, inner, vocab = DESIGN_SIZES[name]
+        layers = args.layers or 2
+        model = Model.random(givopel_config(width, heads, kv_heads, head_dim, inner, layers, vocab), seed=0,
+                             dtype="bfloat16", device="cuda:0")
+        if args.only == "prefill":
+            ms = time_prefill(model, args.prefill_tokens, iters=max(1, args.steps), warmup=args.warmup)
+            print(json.dumps({"design": "givopel", "only": "prefill", "size": name, "layers": layers,
+                              "tokens": args.prefill_tokens, "ms": round(ms, 3)}))
+        else:
+            r = time_decode(model, args.batch, args.context, args.steps, args.warmup)
+            print(json.dumps({"design": "givopel", "only": "decode", "size": name, "layers": layers, "batch": args.batch,
+                              "context": args.context, "ms_per_step": round(r["ms_per_step"], 4)}))
+        return 0
     layers = args.layers or 8
     out = {"design": "givopel", "layers": layers, "prefill_tokens": args.prefill_tokens, "decode_batch": args.batch,
            "decode_context": args.context, "sizes": {}}
