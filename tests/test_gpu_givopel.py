@@ -9,11 +9,12 @@ from givopel_cases import CASES, make_case
 from helpers import random_prompts, scaled_error
 
 pytestmark = pytest.mark.gpu
-# Of the logit scale.  The 32-bit runs are the sharp ones.  In bfloat16 the test models' sharp attention and
-# unit-norm branch outputs multiply a rounding error by about 1.6 with every layer run (the 32-bit error grows
-# at the same rate, from 3e-7 after the first run to 5e-6 after the seventh), so whole models of seven runs
-# get a wider bound than single mechanisms do.
-TOL = {"float32": 2e-5, "bfloat16": 0.1}
+# Of the logit scale.  The 32-bit runs are the sharp ones.  The test models' sharp attention and unit-norm branch
+# outputs multiply a rounding error by about 1.6 with every layer run (measured in 32-bit: 3e-7 of the stream after
+# the first run, 5e-6 after the seventh; in bfloat16 0.003 and 0.075), so whole models of seven runs get wider
+# bounds than single mechanisms do (2e-5 and 3e-2 there).  A wrong key, a lost state or a token that is one off
+# moves the logits by 0.2 or more of their scale.
+TOL = {"float32": 5e-5, "bfloat16": 0.1}
 
 
 @pytest.fixture(scope="module")

@@ -106,7 +106,9 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
     cp_async_commit();
   };
 
-  float S[C2][R];
+  // the state as pairs: the multiply-adds below are the packed 2 x fp32 instructions of sm_100 (each half a true
+  // 32-bit fused multiply-add, rounded to nearest), half as many instructions for the same arithmetic
+  float2 S[C2][R / 2];
   float* sp = a.state + (((size_t)slot * a.n_heads + h) * vdim + j) * dim;  // column j + c is c * dim further
 #pragma unroll
   for (int c = 0; c < C2; ++c) {
@@ -116,11 +118,14 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
       for (int i = 0; i < R; i += 4) {
         float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
         if (live && row_of(i) < dim) t = *reinterpret_cast<const float4*>(sp + (size_t)c * dim + row_of(i));
-        S[c][i] = t.x; S[c][i + 1] = t.y; S[c][i + 2] = t.z; S[c][i + 3] = t.w;
+        S[c][i / 2] = make_float2(t.x, t.y);
+        S[c][i / 2 + 1] = make_float2(t.z, t.w);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < R; ++i) S[c][i] = (live && row_of(i) < dim) ? sp[(size_t)c * dim + row_of(i)] : 0.f;
+      for (int i = 0; i < R; i += 2)
+        S[c][i / 2] = make_float2((live && row_of(i) < dim) ? sp[(size_t)c * dim + row_of(i)] : 0.f,
+                                  (live && row_of(i + 1) < dim) ? sp[(size_t)c * dim + row_of(i + 1)] : 0.f);
     }
   }
   __syncthreads();  // the zero fill is done before the first copies land
@@ -150,63 +155,66 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
       float u[C2];
 #pragma unroll
       for (int c = 0; c < C2; ++c) u[c] = sv[tt * cols + jl + c];
-      float kr[R];
+      float2 kr[R / 2];
 #pragma unroll
       for (int i = 0; i < R; i += 4) {
         const float4 t = pk[(i / 4) * parts];
-        kr[i] = t.x; kr[i + 1] = t.y; kr[i + 2] = t.z; kr[i + 3] = t.w;
+        kr[i / 2] = make_float2(t.x, t.y);
+        kr[i / 2 + 1] = make_float2(t.z, t.w);
       }
       if (DELTA) {
         const float b = sb[tt];
-        float seen[C2][2];
+        float2 seen[C2][2];
 #pragma unroll
-        for (int c = 0; c < C2; ++c) seen[c][0] = seen[c][1] = 0.f;
+        for (int c = 0; c < C2; ++c) seen[c][0] = seen[c][1] = make_float2(0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
           const float4 d = pa[(i / 4) * parts];
 #pragma unroll
           for (int c = 0; c < C2; ++c) {
-            S[c][i] *= d.x; S[c][i + 1] *= d.y; S[c][i + 2] *= d.z; S[c][i + 3] *= d.w;
-            seen[c][0] = fmaf(S[c][i], kr[i], seen[c][0]); seen[c][1] = fmaf(S[c][i + 1], kr[i + 1], seen[c][1]);
-            seen[c][0] = fmaf(S[c][i + 2], kr[i + 2], seen[c][0]); seen[c][1] = fmaf(S[c][i + 3], kr[i + 3], seen[c][1]);
+            S[c][i / 2] = __fmul2_rn(S[c][i / 2], make_float2(d.x, d.y));
+            S[c][i / 2 + 1] = __fmul2_rn(S[c][i / 2 + 1], make_float2(d.z, d.w));
+            seen[c][0] = __ffma2_rn(S[c][i / 2], kr[i / 2], seen[c][0]);
+            seen[c][1] = __ffma2_rn(S[c][i / 2 + 1], kr[i / 2 + 1], seen[c][1]);
           }
         }
 #pragma unroll
         for (int c = 0; c < C2; ++c) {
-          float total = seen[c][0] + seen[c][1];
+          float total = (seen[c][0].x + seen[c][0].y) + (seen[c][1].x + seen[c][1].y);
           for (int o = 1; o < parts; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
           u[c] = b * (u[c] - total);
         }
 #pragma unroll
         for (int c = 0; c < C2; ++c)
 #pragma unroll
-          for (int i = 0; i < R; ++i) S[c][i] = fmaf(kr[i], u[c], S[c][i]);
+          for (int i = 0; i < R / 2; ++i) S[c][i] = __ffma2_rn(kr[i], make_float2(u[c], u[c]), S[c][i]);
       } else {
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
           const float4 d = pa[(i / 4) * parts];
 #pragma unroll
           for (int c = 0; c < C2; ++c) {
-            S[c][i] = fmaf(S[c][i], d.x, kr[i] * u[c]); S[c][i + 1] = fmaf(S[c][i + 1], d.y, kr[i + 1] * u[c]);
-            S[c][i + 2] = fmaf(S[c][i + 2], d.z, kr[i + 2] * u[c]); S[c][i + 3] = fmaf(S[c][i + 3], d.w, kr[i + 3] * u[c]);
+            const float2 uu = make_float2(u[c], u[c]);
+            S[c][i / 2] = __ffma2_rn(S[c][i / 2], make_float2(d.x, d.y), __fmul2_rn(kr[i / 2], uu));
+            S[c][i / 2 + 1] = __ffma2_rn(S[c][i / 2 + 1], make_float2(d.z, d.w), __fmul2_rn(kr[i / 2 + 1], uu));
           }
         }
       }
-      float read[C2][2];
+      float2 read[C2][2];
 #pragma unroll
-      for (int c = 0; c < C2; ++c) read[c][0] = read[c][1] = 0.f;
+      for (int c = 0; c < C2; ++c) read[c][0] = read[c][1] = make_float2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < R; i += 4) {
         const float4 qq = pq[(i / 4) * parts];
 #pragma unroll
         for (int c = 0; c < C2; ++c) {
-          read[c][0] = fmaf(S[c][i], qq.x, read[c][0]); read[c][1] = fmaf(S[c][i + 1], qq.y, read[c][1]);
-          read[c][0] = fmaf(S[c][i + 2], qq.z, read[c][0]); read[c][1] = fmaf(S[c][i + 3], qq.w, read[c][1]);
+          read[c][0] = __ffma2_rn(S[c][i / 2], make_float2(qq.x, qq.y), read[c][0]);
+          read[c][1] = __ffma2_rn(S[c][i / 2 + 1], make_float2(qq.z, qq.w), read[c][1]);
         }
       }
 #pragma unroll
       for (int c = 0; c < C2; ++c) {
-        float total = read[c][0] + read[c][1];
+        float total = (read[c][0].x + read[c][0].y) + (read[c][1].x + read[c][1].y);
         for (int o = 1; o < parts; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         if (part == 0 && j + c < vdim) a.out[(size_t)(t0 + tt) * a.n_heads * vdim + h * vdim + j + c] = total * a.q_scale;
       }
@@ -220,11 +228,14 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
 #pragma unroll
       for (int i = 0; i < R; i += 4)
         if (row_of(i) < dim)
-          *reinterpret_cast<float4*>(sp + (size_t)c * dim + row_of(i)) = make_float4(S[c][i], S[c][i + 1], S[c][i + 2], S[c][i + 3]);
+          *reinterpret_cast<float4*>(sp + (size_t)c * dim + row_of(i)) =
+              make_float4(S[c][i / 2].x, S[c][i / 2].y, S[c][i / 2 + 1].x, S[c][i / 2 + 1].y);
     } else {
 #pragma unroll
-      for (int i = 0; i < R; ++i)
-        if (row_of(i) < dim) sp[(size_t)c * dim + row_of(i)] = S[c][i];
+      for (int i = 0; i < R; i += 2) {
+        if (row_of(i) < dim) sp[(size_t)c * dim + row_of(i)] = S[c][i / 2].x;
+        if (row_of(i + 1) < dim) sp[(size_t)c * dim + row_of(i + 1)] = S[c][i / 2].y;
+      }
     }
   }
 }
