@@ -162,3 +162,49 @@ def test_a_model_without_a_file_is_drawn_from_a_seed(cases):
     a = engine.step([StepEntry(slot, [1, 2, 3, 4], [3])])
     b = engine.step([StepEntry(slot, [5], [0])])
     assert a.shape == (1, config["vocab"]) and bool(a.isfinite().all()) and bool(b.isfinite().all())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_as_a_user_runs_it(cases, tmp_path, dtype):
+    """``bin/trace_run`` on a Givopel folder: five requests of unequal lengths start as one batch and are decoded
+    together, the shorter ones end earlier, and the cache is asked for no more than the tokens they hold (every
+    request's last block of 64 is partly empty)."""
+    import json
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder, config, weights = cases["no-loop"]
+    lengths, tails = [3, 70, 1, 65, 20], [4, 9, 2, 9, 6]
+    prompts = random_prompts(config["vocab"], [k + t for k, t in zip(lengths, tails)], seed=21)
+    want = [_plain(config, weights, p) for p in prompts]
+    steps = [{"step": 0, "entries": [{"id": f"q{i}", "tokens": p[:k], "want": list(range(k))}
+                                     for i, (p, k) in enumerate(zip(prompts, lengths))], "end": []}]
+    for n in range(max(tails)):
+        live = [i for i, t in enumerate(tails) if n < t]
+        steps.append({"step": n + 1, "entries": [{"id": f"q{i}", "tokens": [prompts[i][lengths[i] + n]],
+                                                  "want": [0] if n % 2 == 0 else []} for i in live],
+                      "end": [f"q{i}" for i in live if n == tails[i] - 1]})
+    out = tmp_path / dtype
+    proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", str(out),
+                           "--max-tokens", str(sum(len(p) for p in prompts))],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    got = {i: [] for i in range(len(prompts))}
+    rows = {i: [] for i in range(len(prompts))}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        if not wanted:
+            assert not (out / f"{s['step']}.f32").exists()
+            continue
+        data = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, config["vocab"])
+        assert data.shape[0] == wanted
+        at = 0
+        for e in s["entries"]:
+            i = int(e["id"][1:])
+            first = 0 if s["step"] == 0 else lengths[i] + s["step"] - 1
+            got[i].append(data[at:at + len(e["want"])])
+            rows[i] += [first + w for w in e["want"]]
+            at += len(e["want"])
+    for i in range(len(prompts)):
+        assert scaled_error(np.concatenate(got[i]), want[i][rows[i]]) < TOL[dtype], i

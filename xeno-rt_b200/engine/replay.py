@@ -12,10 +12,17 @@ from .model import Model
 from .step import Engine, StepEntry
 
 
+SPARE_BLOCKS = 64  # beyond ``max_tokens``: every live request may hold one cache block that is not full
+
+
 class Replayer:
     def __init__(self, model_folder: str, dtype: str, max_tokens: int, device: str = "cuda:0", model=None):
+        """``max_tokens``: the most tokens that live requests hold at any time.  The cache is made of blocks of
+        64 positions and a request's last block is rarely full, so room for ``SPARE_BLOCKS`` more blocks (and
+        at least that many live requests) is added."""
+        from ..cache import BLOCK_TOKENS
         self.model = model if model is not None else Model.load(model_folder, dtype=dtype, device=device)
-        self.engine = Engine(self.model, max_tokens)
+        self.engine = Engine(self.model, max(1, int(max_tokens)) + SPARE_BLOCKS * BLOCK_TOKENS)
         self.slots: dict[str, int] = {}
 
     def run_step(self, record: dict):
