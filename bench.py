@@ -306,15 +306,15 @@ def givopel_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: 
     keys and values of ``head_dim``, half as many q/k heads, 4 taps) and gated linear attention (``heads`` / 2
     heads, keys of ``head_dim``, values of twice that), every layer with a feed-forward of ``inner``; the whole
     stack is one loop that runs once (so that the step which begins a pass is in the timing)."""
-    rot = {"base": 1000000.0, "dims": head_dim, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 500000.0, "dims": head_dim, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}
     parallel = {"type": "parallel", "mlp": {"kind": "dense", "ff": inner}, "mixer": {
         "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "rot": rot},
         "right": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": head_dim, "vdim": head_dim, "conv": 4,
                   "decay_rank": 64, "gate_rank": 64}}}
     gla = {"type": "gla", "mlp": {"kind": "dense", "ff": inner},
-           "mixer": {"heads": max(1, heads // 2), "dim": head_dim, "vdim": 2 * head_dim, "tau": 16.0, "decay_rank": 64}}
-    return {"architecture": "Givopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
-            "logit_softcap": 30.0, "loop": {"start": 0, "stop": layers, "times": 1},
+           "mixer": {"heads": max(1, heads // 2), "dim": head_dim, "vdim": 2 * head_dim, "tau": 8.0, "decay_rank": 64}}
+    return {"architecture": "Givopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "logit_softcap": 50.0, "loop": {"start": 0, "stop": layers, "times": 1},
             "layers": [parallel if i % 2 == 0 else gla for i in range(layers)]}
 
 

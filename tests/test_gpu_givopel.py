@@ -85,7 +85,7 @@ def test_unequal_batches_equal_each_request_alone_and_slots_are_used_again(cases
     decode = 12
     prompts = random_prompts(config["vocab"], [k + decode for k in lengths], seed=4)
     want = [_plain(config, weights, p) for p in prompts]
-    for round_ in range(2):  # the second round takes the slots, blocks and states that the first gave back
+    for turn in range(2):  # the second turn takes the slots, blocks and states that the first gave back
         slots = [engine.open_slot() for _ in prompts]
         got = [[] for _ in prompts]
         out = engine.step([StepEntry(s, p[:k], list(range(k))) for s, p, k in zip(slots, prompts, lengths)]).cpu().numpy()
@@ -104,7 +104,7 @@ def test_unequal_batches_equal_each_request_alone_and_slots_are_used_again(cases
             engine.close_slot(slots[i])
         for i in range(len(prompts)):
             rows = np.concatenate(got[i])
-            assert scaled_error(rows, want[i][:len(rows)]) < tol, (round_, i)
+            assert scaled_error(rows, want[i][:len(rows)]) < tol, (turn, i)
         engine.cache.check()
     engine.check_errors()
 

@@ -189,7 +189,7 @@ def test_layer_norm_with_gathered_rows(width):
 
 
 @pytest.mark.parametrize("scaling", [None, {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 2.0},
-                                     {"factor": 2.0, "original": 1000, "fast": 32.0, "slow": 1.0},
+                                     {"factor": 3.0, "original": 1000, "fast": 20.0, "slow": 0.5},
                                      {"factor": 16.0, "original": 4096, "fast": 1.0, "slow": 1.0}])
 def test_blended_rotation_table(scaling):
     from types import SimpleNamespace
