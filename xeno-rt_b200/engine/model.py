@@ -151,8 +151,8 @@ class Model:
         crates/xrt-models/src/llama.rs:432-613; the final norm and the output matrix see only the
         wanted rows (llama.rs:814-819 does so for the last token)."""
         x = x0 = self.embedding.forward(ctx.token_ids, self.error_flag)
-        if self.stream_parts:
-            x = x0.clone()  # layers change x in place; stream parts read what the embedding gave
+        if self.stream_parts and self.spec.schedule[0].before is None:
+            x = x0.clone()  # layers change x in place before the first stream part reads what the embedding gave
         for i, place in enumerate(self.spec.schedule):
             owns = place.cache_from is None
             if place.before is not None:

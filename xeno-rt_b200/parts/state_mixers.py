@@ -39,6 +39,13 @@ class _StateMixer:
         return linear(self.heads_out(h, ctx, store, owns_cache), self.w_o, out_dtype=torch.float32)
 
     @staticmethod
+    def _rows(ctx):
+        """How to make a buffer that the per-sequence kernels fill: they skip rows of no sequence (the padding rows
+        of a captured step), which must then hold zeros and not whatever the memory held."""
+        padded = getattr(ctx, "captured", False) or sum(ctx.new_lens) < ctx.n_tokens  # a captured step is replayed with padding rows
+        return torch.zeros if padded else torch.empty
+
+    @staticmethod
     def _owning(owns_cache):
         if not owns_cache:
             raise ConfigError("a mixer with a state cannot read another place's: the state is what the tokens left there")
@@ -85,7 +92,7 @@ class GatedLinearAttention(_StateMixer):
         p = linear(h, self.w_in, out_dtype=torch.float32)
         decay = linear(linear(h, self.w_a1, out_dtype=self.act_dtype), self.w_a2, out_dtype=torch.float32)
         ops.decay_from_gate(decay, self.a2_bias, nh, kd, self.tau)
-        o = torch.zeros((n, nh * vd), dtype=torch.float32, device=h.device)  # rows of no sequence stay zero
+        o = self._rows(ctx)((n, nh * vd), dtype=torch.float32, device=h.device)
         ops.state_scan(o, p, p[:, nh * kd:], p[:, 2 * nh * kd:], decay, None, store.state, ctx.cu_seqlens, ctx.seq_slot,
                        nh, nh, kd, vd, q_scale=kd ** -0.5, max_new=ctx.max_new)
         y = torch.empty((n, nh * vd), dtype=self.act_dtype, device=h.device)
@@ -158,11 +165,11 @@ class GatedDeltaRule(_StateMixer):
         decay = linear(low[:, :self.decay_rank], self.w_a2, out_dtype=torch.float32)
         gate = linear(low[:, self.decay_rank:], self.w_g2, out_dtype=torch.float32)
         ops.decay_from_step(decay, self.dt_bias, self.a_log, nh, kd)
-        qkv = torch.zeros((n, self.channels), dtype=torch.float32, device=h.device)
+        qkv = self._rows(ctx)((n, self.channels), dtype=torch.float32, device=h.device)
         conv_state = store[1].state if self.taps > 1 else None
         ops.short_conv(qkv, p, self.conv, conv_state, ctx.cu_seqlens, ctx.seq_slot, ctx.max_new, "silu")
         ops.unit_heads(qkv, 2 * nq, kd, self.UNIT_EPS, scaled_heads=nq, scale=kd ** -0.5)
-        o = torch.zeros((n, nh * vd), dtype=torch.float32, device=h.device)
+        o = self._rows(ctx)((n, nh * vd), dtype=torch.float32, device=h.device)
         ops.state_scan(o, qkv, qkv[:, nq * kd:], qkv[:, 2 * nq * kd:], decay, p[:, self.channels:], store[0].state,
                        ctx.cu_seqlens, ctx.seq_slot, nh, nq, kd, vd, delta=True, max_new=ctx.max_new)
         y = torch.empty((n, nh * vd), dtype=self.act_dtype, device=h.device)
