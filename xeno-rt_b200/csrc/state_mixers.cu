@@ -478,16 +478,10 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
     else if (vec) XRT_SCAN(RR, CC, false, true);               \
     else XRT_SCAN(RR, CC, false, false);                       \
   } while (0)
-  if (per_lane == 1) {
-    if (R == 8) XRT_SCAN_R(8, 1);
-    else if (R == 16) XRT_SCAN_R(16, 1);
-    else if (R == 64) XRT_SCAN_R(64, 1);
-    else XRT_SCAN_R(32, 1);
-  } else {
-    if (R == 8) XRT_SCAN_R(8, 4);
-    else if (R == 16) XRT_SCAN_R(16, 4);
-    else XRT_SCAN_R(32, 2);
-  }
+  if (R == 8) XRT_SCAN_R(8, 1);
+  else if (R == 16) XRT_SCAN_R(16, 1);
+  else if (R == 64) XRT_SCAN_R(64, 1);
+  else XRT_SCAN_R(32, 1);
 #undef XRT_SCAN_R
 #undef XRT_SCAN
   return xrt::launch_status();
