@@ -62,7 +62,16 @@ class _KVGroup:
         self.table_host = np.full((max_slots, blocks_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, blocks_per_seq), -1, dtype=torch.int32, device=device)
         self.dirty: set[int] = set()
-        self.first_block = [0] * max_slots  # blocks before it were given back (windowed groups)
+        self.first_block = [0] * max_slots  # blocks before it were given back (windowed groups) ...
+        # ... but for the blocks that hold the first ``keep_first`` positions, which stay visible behind the window
+        self.kept_blocks = 0
+        if need.window is not None and need.keep_first > 0:
+            self.kept_blocks = (int(need.keep_first) + BLOCK_TOKENS - 1) // BLOCK_TOKENS
+
+    def held_blocks(self, slot: int, n: int) -> list:
+        """The indices among a sequence's first ``n`` blocks that it still holds."""
+        given_back_to = max(self.first_block[slot], self.kept_blocks)
+        return [b for b in range(n) if b < self.kept_blocks or b >= given_back_to]
 
     def blocks_behind_the_window(self, length: int) -> int:
         """How many leading blocks hold no key that a token at position ``length`` or later sees:
@@ -201,7 +210,7 @@ class Cache:
             raise CacheError(f"slot {slot} is not open (closed twice, or never opened)")
         n = self._n_seq_blocks[slot]
         for group in self.kv_groups:
-            group.allocator.give_back(int(b) for b in group.table_host[slot, group.first_block[slot]:n])
+            group.allocator.give_back(int(group.table_host[slot, b]) for b in group.held_blocks(slot, n))
             group.table_host[slot, :n] = -1
             group.first_block[slot] = 0
             group.dirty.add(slot)
@@ -272,7 +281,7 @@ class Cache:
         self.lengths[slot] += n_new
         for group in self.kv_groups:
             done = min(group.blocks_behind_the_window(self.lengths[slot]), self._n_seq_blocks[slot])
-            first = group.first_block[slot]
+            first = max(group.first_block[slot], min(group.kept_blocks, self._n_seq_blocks[slot]))
             if done > first:
                 # Kernels already launched still read the old table and the old blocks: the table
                 # changes with the next flush and the blocks are written again only by later steps.
@@ -315,13 +324,15 @@ class Cache:
                 row = group.table_host[slot]
                 n = self._n_seq_blocks[slot] if self.slots.is_open(slot) else 0
                 first = group.first_block[slot] if self.slots.is_open(slot) else 0
-                if (row[n:] != -1).any() or (row[:first] != -1).any():
+                mine = group.held_blocks(slot, n) if self.slots.is_open(slot) else []
+                gone = [b for b in range(n) if b not in set(mine)]
+                if (row[n:] != -1).any() or (row[gone] != -1).any():
                     raise CacheError(f"slot {slot} lists blocks beyond what it holds")
-                if (row[first:n] < 0).any():
+                if (row[mine] < 0).any():
                     raise CacheError(f"slot {slot} misses a block that it should hold")
                 if first > group.blocks_behind_the_window(self.lengths[slot]):
                     raise CacheError(f"slot {slot} gave back a block that its window still covers")
-                held.extend(int(b) for b in row[first:n])
+                held.extend(int(b) for b in row[mine])
             if len(held) != len(set(held)):
                 raise CacheError("a block is listed by two sequences")
             if len(held) != group.allocator.held:

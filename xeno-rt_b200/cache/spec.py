@@ -17,10 +17,12 @@ class KVNeed:
     """Keys and values indexed by position: [kv head][position][head_dim] for each sequence.
     ``window`` = None keeps every position; a number keeps that many most recent positions
     visible (the storage of a windowed group is its own, so it can be sized and released apart
-    from the groups that keep everything)."""
+    from the groups that keep everything); with a window, ``keep_first`` positions at a sequence's start stay
+    visible (and their blocks held) however far the sequence moves."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

@@ -17,7 +17,29 @@ __global__ void swiglu_kernel(TO* __restrict__ out, const TI* __restrict__ gate_
   }
 }
 
+// Squared relu: out[i] = max(x[i], 0)^2 (the activation of a feed-forward without a gate).
+template <typename TO>
+__global__ void relu_squared_kernel(TO* __restrict__ out, const float* __restrict__ x, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(x[i], 0.f);
+    out[i] = from_float<TO>(v * v);
+  }
+}
+
 }  // namespace xrt
+
+XRT_EXPORT int xrt_relu_squared(void* out, const float* x, int n_tokens, int width, int out_dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  const size_t total = (size_t)n_tokens * width;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  XRT_DISPATCH_DTYPE(out_dtype, TO, {
+    xrt::launch_kernel(xrt::relu_squared_kernel<TO>, dim3(blocks), dim3(256), 0, stream, (TO*)out, x, total);
+  });
+  return xrt::launch_status();
+}
 
 XRT_EXPORT int xrt_swiglu(void* out, const void* gate_up, int n_tokens, int width, int in_dtype,
                           int out_dtype, cudaStream_t stream) {

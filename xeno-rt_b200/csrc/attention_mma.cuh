@@ -188,11 +188,20 @@ __device__ __forceinline__ void attend_16_keys(SoftmaxState<D_TILES>& st, const 
 // a call, which is what makes long steps cheap), and the product with the same rows of the value
 // tile.  `masked` (uniform over the warp) says whether any key of the range may be hidden from a
 // row; without it the comparisons are skipped.
-template <int D_TILES, int KEY_TILES>
+// SCORED: the scores pass the layer's options (ScoreOptions) in 32-bit before the softmax.  `scale_log2` is
+// then the plain scale, `slope` this head's distance slope, `softcap` the cap (0: none), and a key below `keep_first`
+// is visible to a row even before the row's key_lo.  A row's own position is key_hi - 1.
+struct ScoredRow {
+  float softcap = 0.f;
+  float slope = 0.f;
+  int keep_first = 0;
+};
+
+template <int D_TILES, int KEY_TILES, bool SCORED = false>
 __device__ __forceinline__ void attend_keys(SoftmaxState<D_TILES>& st, const uint32_t (*qf)[4],
                                             const unsigned char* ks_tile, const unsigned char* vs_tile, int key_row,
                                             int key_abs, const int (&key_lo)[2], const int (&key_hi)[2], bool masked,
-                                            int head_dim, float scale_log2) {
+                                            int head_dim, float scale_log2, const ScoredRow scored = ScoredRow()) {
   static_assert(KEY_TILES % 2 == 0, "keys come in groups of 16");
   const int lane = threadIdx.x & 31, t = lane & 3;
   const int row_bytes = tile_row_bytes(head_dim);
@@ -222,11 +231,20 @@ __device__ __forceinline__ void attend_keys(SoftmaxState<D_TILES>& st, const uin
     for (int e = 0; e < 4; ++e) {
       const int row = e >> 1;
       bool live = true;
-      if (masked) {
+      if (SCORED) {
         const int key = key_abs + nt * 8 + 2 * t + (e & 1);
-        live = key >= key_lo[row] && key < key_hi[row];
+        live = key < key_hi[row] && (key >= key_lo[row] || key < scored.keep_first);
+        float v = s[nt][e] * scale_log2;
+        if (scored.softcap > 0.f) v = scored.softcap * tanhf(v / scored.softcap);
+        v -= scored.slope * (float)(key_hi[row] - 1 - key);
+        s[nt][e] = live ? v * 1.4426950408889634f : -INFINITY;
+      } else {
+        if (masked) {
+          const int key = key_abs + nt * 8 + 2 * t + (e & 1);
+          live = key >= key_lo[row] && key < key_hi[row];
+        }
+        s[nt][e] = live ? s[nt][e] * scale_log2 : -INFINITY;
       }
-      s[nt][e] = live ? s[nt][e] * scale_log2 : -INFINITY;
       tile_max[row] = fmaxf(tile_max[row], s[nt][e]);
     }
   float corr[2];

@@ -18,13 +18,16 @@ namespace xrt {
 constexpr int PRE_WARPS = 4;
 constexpr int PRE_ROWS = PRE_WARPS * 16;
 
-template <int HD_MAX>
+// SCORED: the layer's score options (common.cuh) are on: kept first keys behind the window, a tanh cap, a distance
+// slope.  The tiles of the kept keys are walked before the window's.
+template <int HD_MAX, bool SCORED>
 __global__ void __launch_bounds__(PRE_WARPS * 32)
 attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
                          const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, const int* __restrict__ block_table, int max_blocks,
-                         int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window) {
+                         int n_heads, int n_kv_heads, int head_dim, float scale_log2, int window,
+                         const ScoreOptions opt) {
   constexpr int D_TILES = HD_MAX / 8;
   extern __shared__ __align__(16) unsigned char smem[];
   // later query tiles walk more keys: they are scheduled first, the longest tiles of all heads and of all the step's
@@ -69,7 +72,16 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int block_hi = start + last_row + 1;                                        // exclusive
   const int block_lo = window > 0 ? max(0, start + row0 + 1 - window) : 0;
   const int first_tile = block_lo / XRT_BLOCK_TOKENS;
-  const int n_tiles = (block_hi + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS - first_tile;
+  // tiles of keys that stay visible behind the window come first; a tile is walked once
+  const int keep_tiles = SCORED ? min((opt.keep_first + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS, first_tile) : 0;
+  const int n_tiles = (block_hi + XRT_BLOCK_TOKENS - 1) / XRT_BLOCK_TOKENS - first_tile + keep_tiles;
+  auto tile_at = [&](int i) { return i < keep_tiles ? i : first_tile + i - keep_tiles; };
+  ScoredRow scored;
+  if (SCORED) {
+    scored.softcap = opt.softcap;
+    scored.keep_first = opt.keep_first;
+    scored.slope = opt.distance_rate > 0.f ? exp2f(-opt.distance_rate * (float)(head + 1) / (float)n_heads) : 0.f;
+  }
   // the warp's own range (uniform over the warp): rows warp*16 .. +16
   const int warp_first_row = row0 + warp * 16;
   const int warp_last_row = min(warp_first_row + 15, n_new - 1);
@@ -85,7 +97,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   TileCopier copier;
   copier.init(head_dim);
   auto issue_tile = [&](int tile_index, int buffer) {
-    const int key0 = (first_tile + tile_index) * XRT_BLOCK_TOKENS;
+    const int key0 = tile_at(tile_index) * XRT_BLOCK_TOKENS;
     const int block = blocks[key0 / XRT_BLOCK_TOKENS];
     const size_t base = ((size_t)block * n_kv_heads + kv_head) * head_stride;
     const int live = min(XRT_BLOCK_TOKENS, block_hi - key0);
@@ -101,12 +113,13 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
     if (i + 1 < n_tiles) { issue_tile(i + 1, (i + 1) & 1); cp_async_wait<1>(); }
     else cp_async_wait<0>();
     __syncthreads();
-    const int key0 = (first_tile + i) * XRT_BLOCK_TOKENS;
+    const int key0 = tile_at(i) * XRT_BLOCK_TOKENS;
     // uniform over the warp: does the tile hold any key this warp's rows see, and may it hide one?
-    if (key0 < warp_hi && key0 + XRT_BLOCK_TOKENS > warp_lo) {
+    if (key0 < warp_hi && (key0 + XRT_BLOCK_TOKENS > warp_lo || (SCORED && key0 < opt.keep_first))) {
       const bool masked = partial_warp || key0 + XRT_BLOCK_TOKENS > warp_min_hi || key0 < warp_max_lo;
-      attend_keys<D_TILES, XRT_BLOCK_TOKENS / 8>(st, qf, k_tiles + (i & 1) * tile_bytes, v_tiles + (i & 1) * tile_bytes,
-                                                 0, key0, key_lo, key_hi, masked, head_dim, scale_log2);
+      attend_keys<D_TILES, XRT_BLOCK_TOKENS / 8, SCORED>(st, qf, k_tiles + (i & 1) * tile_bytes,
+                                                         v_tiles + (i & 1) * tile_bytes, 0, key0, key_lo, key_hi, masked,
+                                                         head_dim, scale_log2, scored);
     }
     __syncthreads();
   }
@@ -131,13 +144,13 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   }
 }
 
-template <int HD_MAX>
-int launch_prefill(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
+template <int HD_MAX, bool SCORED>
+int launch_prefill_of(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
                    const int* cu_seqlens, const int* seq_slot, const int* seq_start, const int* block_table,
                    int max_blocks, int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
-                   int window, cudaStream_t stream) {
+                   int window, const ScoreOptions& opt, cudaStream_t stream) {
   const int smem = 4 * XRT_BLOCK_TOKENS * (head_dim * 2 + 16);
-  auto kernel = attention_prefill_kernel<HD_MAX>;
+  auto kernel = attention_prefill_kernel<HD_MAX, SCORED>;
   static int smem_allowed = 0;
   if (smem > 48 * 1024 && smem > smem_allowed) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -147,8 +160,20 @@ int launch_prefill(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat
   dim3 grid(n_heads, n_seqs, (max_new + PRE_ROWS - 1) / PRE_ROWS);
   kernel<<<grid, PRE_WARPS * 32, smem, stream>>>(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table,
                                                 max_blocks, n_heads, n_kv_heads, head_dim,
-                                                scale * 1.4426950408889634f, window);
+                                                SCORED ? scale : scale * 1.4426950408889634f, window, opt);
   return launch_status();
+}
+
+template <int HD_MAX>
+int launch_prefill(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
+                   const int* cu_seqlens, const int* seq_slot, const int* seq_start, const int* block_table,
+                   int max_blocks, int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
+                   int window, const ScoreOptions& opt, cudaStream_t stream) {
+  if (opt.keep_first > 0 || opt.softcap > 0.f || opt.distance_rate > 0.f)
+    return launch_prefill_of<HD_MAX, true>(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_blocks,
+                                           n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, window, opt, stream);
+  return launch_prefill_of<HD_MAX, false>(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_blocks,
+                                          n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, window, opt, stream);
 }
 
 }  // namespace xrt
@@ -160,7 +185,12 @@ int launch_prefill(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat
 XRT_EXPORT int xrt_attention_prefill(void* out, const void* q, const void* k_pool, const void* v_pool,
                                      const int* cu_seqlens, const int* seq_slot, const int* seq_start,
                                      const int* block_table, int max_blocks, int n_seqs, int max_new, int n_heads,
-                                     int n_kv_heads, int head_dim, float scale, int window, cudaStream_t stream) {
+                                     int n_kv_heads, int head_dim, float scale, int window, int keep_first,
+                                     float softcap, float distance_rate, cudaStream_t stream) {
+  xrt::ScoreOptions opt;
+  opt.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
+  opt.softcap = softcap;
+  opt.distance_rate = distance_rate;
   if (n_seqs < 0 || max_new < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return XRT_ERR_ARGUMENT;
   if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256 || n_seqs > 65535 || (max_new + xrt::PRE_ROWS - 1) / xrt::PRE_ROWS > 65535) return XRT_ERR_UNSUPPORTED;
   if (n_seqs == 0 || max_new == 0) return XRT_OK;
@@ -170,7 +200,7 @@ XRT_EXPORT int xrt_attention_prefill(void* out, const void* q, const void* k_poo
   auto* vp = (const __nv_bfloat16*)v_pool;
 #define XRT_PREFILL(HD) return xrt::launch_prefill<HD>(o, qp, kp, vp, cu_seqlens, seq_slot, seq_start, block_table, \
                                                        max_blocks, n_seqs, max_new, n_heads, n_kv_heads, head_dim,  \
-                                                       scale, window, stream)
+                                                       scale, window, opt, stream)
   if (head_dim <= 32) XRT_PREFILL(32);
   if (head_dim <= 64) XRT_PREFILL(64);
   if (head_dim <= 128) XRT_PREFILL(128);

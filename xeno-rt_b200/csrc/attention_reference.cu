@@ -8,6 +8,9 @@
 //   s_j = dot(q, k_j) / sqrt(head_dim), j = 0 .. pos (the causal mask is the bound)  :506, 736-751
 //   online softmax: running maximum and sum, rescale on a new maximum, divide at the end  :514-574
 // `window` > 0 keeps only keys with pos - j < window (absent in the reference; 0 = all keys).
+// Further options on the scores, all 32-bit and all off at 0 (ScoreOptions in common.cuh): the first `keep_first`
+// keys of a sequence stay visible behind the window; s <- cap * tanh(s / cap); s <- s - slope_h * (pos - j) with
+// slope_h = 2^(-rate (h + 1) / n_heads).
 #include "common.cuh"
 
 namespace xrt {
@@ -17,7 +20,7 @@ __global__ void attention_reference_kernel(
     TO* __restrict__ out, const TQ* __restrict__ q, const TC* __restrict__ k_pool,
     const TC* __restrict__ v_pool, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
     const int* __restrict__ block_table, int max_blocks, int n_heads, int n_kv_heads, int head_dim,
-    float scale, int window) {
+    float scale, int window, const ScoreOptions opt) {
   extern __shared__ float q_staged[];  // [warps][head_dim]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -41,19 +44,24 @@ __global__ void attention_reference_kernel(
   for (int j = 0; j < MAX_PER_LANE; ++j) acc[j] = 0.f;
   float running_max = -INFINITY, running_sum = 0.f;
   const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kept = min(opt.keep_first, first_key);  // keys [0, kept) lie behind the window and stay visible
+  const float slope = opt.distance_rate > 0.f ? exp2f(-opt.distance_rate * (float)(head + 1) / (float)n_heads) : 0.f;
   const int* blocks = block_table + (size_t)slot * max_blocks;
 
-  for (int base = (first_key / 32) * 32; base <= pos; base += 32) {
+  // keys [lo, hi) of the 32 that start at `base`
+  auto tile_of_keys = [&](int base, int lo, int hi) {
     const int block = blocks[base / XRT_BLOCK_TOKENS];
     const size_t tile = (((size_t)block * n_kv_heads + kv_head) * XRT_BLOCK_TOKENS + base % XRT_BLOCK_TOKENS) * head_dim;
     const int key = base + lane;
-    const bool live = key >= first_key && key <= pos;
+    const bool live = key >= lo && key < hi;
     float s = -INFINITY;
     if (live) {
       const TC* kr = k_pool + tile + (size_t)lane * head_dim;
       float dot = 0.f;
       for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
       s = dot * scale;
+      if (opt.softcap > 0.f) s = opt.softcap * tanhf(s / opt.softcap);
+      s -= slope * (float)(pos - key);
     }
     const float tile_max = warp_max(s);
     const float new_max = fmaxf(running_max, tile_max);
@@ -63,8 +71,8 @@ __global__ void attention_reference_kernel(
     running_max = new_max;
 #pragma unroll
     for (int j = 0; j < MAX_PER_LANE; ++j) acc[j] *= correction;
-    const int n_live = min(32, pos - base + 1);
-    for (int kk = 0; kk < n_live; ++kk) {
+    const int n_live = min(32, hi - base);
+    for (int kk = max(0, lo - base); kk < n_live; ++kk) {
       const float pk = __shfl_sync(0xffffffffu, p, kk);
       const TC* vr = v_pool + tile + (size_t)kk * head_dim;
 #pragma unroll
@@ -73,7 +81,9 @@ __global__ void attention_reference_kernel(
         if (d < head_dim) acc[j] = fmaf(pk, to_float(vr[d]), acc[j]);
       }
     }
-  }
+  };
+  for (int base = 0; base < kept; base += 32) tile_of_keys(base, 0, kept);
+  for (int base = (first_key / 32) * 32; base <= pos; base += 32) tile_of_keys(base, first_key, pos + 1);
   const float inv = 1.0f / running_sum;
 #pragma unroll
   for (int j = 0; j < MAX_PER_LANE; ++j) {
@@ -88,8 +98,12 @@ __global__ void attention_reference_kernel(
 XRT_EXPORT int xrt_attention_reference(void* out, const void* q, const void* k_pool, const void* v_pool,
                                        const int* tok_slot, const int* tok_pos, const int* block_table,
                                        int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                       float scale, int window, int q_dtype, int cache_dtype, int out_dtype,
-                                       cudaStream_t stream) {
+                                       float scale, int window, int keep_first, float softcap, float distance_rate,
+                                       int q_dtype, int cache_dtype, int out_dtype, cudaStream_t stream) {
+  xrt::ScoreOptions opt;
+  opt.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
+  opt.softcap = softcap;
+  opt.distance_rate = distance_rate;
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_heads % n_kv_heads != 0)
     return XRT_ERR_ARGUMENT;
   if (head_dim > 256) return XRT_ERR_UNSUPPORTED;
@@ -102,7 +116,7 @@ XRT_EXPORT int xrt_attention_reference(void* out, const void* q, const void* k_p
       XRT_DISPATCH_DTYPE(out_dtype, TO, {
         xrt::attention_reference_kernel<TQ, TC, TO, 8><<<grid, warps * 32, smem, stream>>>(
             (TO*)out, (const TQ*)q, (const TC*)k_pool, (const TC*)v_pool, tok_slot, tok_pos, block_table,
-            max_blocks, n_heads, n_kv_heads, head_dim, scale, window);
+            max_blocks, n_heads, n_kv_heads, head_dim, scale, window, opt);
       });
     });
   });

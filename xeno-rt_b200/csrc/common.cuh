@@ -55,6 +55,15 @@ struct RowScale {
   float eps = 0.f;
 };
 
+// What an attention layer may do to its scores beside the scale, the causal bound and the window (0 = off):
+// keys [0, keep_first) stay visible behind a window; s <- softcap * tanh(s / softcap); then
+// s <- s - slope_h * (query position - key position), slope_h = 2^(-distance_rate * (h + 1) / n_heads).
+struct ScoreOptions {
+  int keep_first = 0;
+  float softcap = 0.f;
+  float distance_rate = 0.f;
+};
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -1,0 +1,144 @@
+// A feed-forward made of many small gated experts of which every token uses a few.
+//
+//   routing   from the router's 32-bit logits z (bias added here): the `top` largest (the lower index wins a tie),
+//             weights = softmax over those alone
+//   expert    g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha g) * (u + 1),
+//             result W_down y, times the token's weight for that expert
+//
+// The experts' matrices lie one after another: w_in [experts][gate rows | up rows][width], w_out [experts][width][ff].
+// xrt_moe_experts computes every (token, choice) pair in a block of its own and writes out[choice][token][width];
+// whoever follows adds a token's choices in index order, so the sum has one order whatever else is in the step.
+#include "common.cuh"
+
+namespace xrt {
+
+// One warp a token.  Lane l holds logits l, l + 32, ...
+template <int PER_LANE>
+__global__ void moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits,
+                                 const float* __restrict__ bias, int n_tokens, int n_experts, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  float z[PER_LANE];
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    z[i] = e < n_experts ? logits[(size_t)t * n_experts + e] + (bias != nullptr ? bias[e] : 0.f) : -INFINITY;
+  }
+  float first = 0.f, sum = 0.f, mine = 0.f;  // lane c keeps the c-th choice's exponential
+  int mine_id = 0;
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (z[i] > best || (z[i] == best && e < best_e && z[i] > -INFINITY)) { best = z[i]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    }
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i)
+      if (lane + 32 * i == best_e) z[i] = -INFINITY;  // taken
+    if (c == 0) first = best;
+    const float p = expf(best - first);  // the first choice is the largest logit
+    sum += p;
+    if (lane == c) { mine = p; mine_id = best_e; }
+  }
+  if (lane < top) {
+    ids[(size_t)t * top + lane] = mine_id;
+    weights[(size_t)t * top + lane] = mine / sum;
+  }
+}
+
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(256)
+moe_experts_kernel(float* __restrict__ out, const TX* __restrict__ h, const TW* __restrict__ w_in,
+                   const TW* __restrict__ w_out, const int* __restrict__ ids, const float* __restrict__ weights,
+                   int n_tokens, int width, int ff, int top, float limit, float alpha) {
+  extern __shared__ float staged[];  // h [width] | y [ff]
+  float* hs = staged;
+  float* ys = staged + width;
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, c = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int e = ids[(size_t)t * top + c];
+  const float weight = weights[(size_t)t * top + c];
+  for (int k = threadIdx.x; k < width; k += blockDim.x) hs[k] = to_float(h[(size_t)t * width + k]);
+  __syncthreads();
+  const TW* gate = w_in + (size_t)e * 2 * ff * width;
+  const TW* up = gate + (size_t)ff * width;
+  for (int j = warp; j < ff; j += n_warps) {
+    const TW* gr = gate + (size_t)j * width;
+    const TW* ur = up + (size_t)j * width;
+    float g = 0.f, u = 0.f;
+    for (int k = lane; k < width; k += 32) {
+      g = fmaf(to_float(gr[k]), hs[k], g);
+      u = fmaf(to_float(ur[k]), hs[k], u);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      ys[j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+  }
+  __syncthreads();
+  const TW* down = w_out + (size_t)e * width * ff;
+  float* dst = out + ((size_t)c * n_tokens + t) * width;
+  for (int r = warp; r < width; r += n_warps) {
+    const TW* dr = down + (size_t)r * ff;
+    float acc = 0.f;
+    for (int k = lane; k < ff; k += 32) acc = fmaf(to_float(dr[k]), ys[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) dst[r] = weight * acc;
+  }
+}
+
+}  // namespace xrt
+
+// logits [T, experts] float32 (without the bias); ids [T, top] int32 and weights [T, top] float32 are written.
+XRT_EXPORT int xrt_moe_route(int* ids, float* weights, const float* logits, const float* bias, int n_tokens,
+                             int n_experts, int top, cudaStream_t stream) {
+  if (n_tokens < 0 || n_experts <= 0 || top <= 0 || top > n_experts) return XRT_ERR_ARGUMENT;
+  if (top > 32 || n_experts > 512) return XRT_ERR_UNSUPPORTED;
+  if (n_tokens == 0) return XRT_OK;
+  const dim3 grid((n_tokens + 3) / 4), block(128);
+  if (n_experts <= 32) xrt::launch_kernel(xrt::moe_route_kernel<1>, grid, block, 0, stream, ids, weights, logits, bias, n_tokens, n_experts, top);
+  else if (n_experts <= 64) xrt::launch_kernel(xrt::moe_route_kernel<2>, grid, block, 0, stream, ids, weights, logits, bias, n_tokens, n_experts, top);
+  else if (n_experts <= 128) xrt::launch_kernel(xrt::moe_route_kernel<4>, grid, block, 0, stream, ids, weights, logits, bias, n_tokens, n_experts, top);
+  else if (n_experts <= 256) xrt::launch_kernel(xrt::moe_route_kernel<8>, grid, block, 0, stream, ids, weights, logits, bias, n_tokens, n_experts, top);
+  else xrt::launch_kernel(xrt::moe_route_kernel<16>, grid, block, 0, stream, ids, weights, logits, bias, n_tokens, n_experts, top);
+  return xrt::launch_status();
+}
+
+// out [top, T, width] float32; h [T, width]; w_in [experts * 2 * ff, width]; w_out [experts * width, ff].
+XRT_EXPORT int xrt_moe_experts(float* out, const void* h, const void* w_in, const void* w_out, const int* ids,
+                               const float* weights, int n_tokens, int width, int ff, int top, float limit, float alpha,
+                               int h_dtype, int w_dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0 || ff <= 0 || top <= 0) return XRT_ERR_ARGUMENT;
+  if (top > 65535) return XRT_ERR_UNSUPPORTED;
+  if (n_tokens == 0) return XRT_OK;
+  const size_t smem = (size_t)(width + ff) * sizeof(float);
+  if (smem > 200 * 1024) return XRT_ERR_UNSUPPORTED;
+  XRT_DISPATCH_DTYPE(h_dtype, TX, {
+    XRT_DISPATCH_DTYPE(w_dtype, TW, {
+      auto kernel = xrt::moe_experts_kernel<TX, TW>;
+      if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+      }
+      xrt::launch_kernel(kernel, dim3(n_tokens, top), dim3(256), smem, stream, out, (const TX*)h, (const TW*)w_in,
+                         (const TW*)w_out, ids, weights, n_tokens, width, ff, top, limit, alpha);
+    });
+  });
+  return xrt::launch_status();
+}

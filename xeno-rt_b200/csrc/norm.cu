@@ -188,7 +188,62 @@ __global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__
     dst[c] = from_float<TO>(((xr[c] - mean) * inv) * to_float(w[c]));
 }
 
+// Layer norm with a weight and an optional bias over the sum of `n_parts` inputs (x + p * part_stride, added in index
+// order), y = (x - mean) / sqrt(var + eps) * w + b.  With `residual` the result is added to that 32-bit row instead of
+// written to `out`: a norm that follows a sublayer, and the residual sum, in one pass.  The row is kept in shared memory.
+template <typename TO>
+__global__ void layernorm_affine_kernel(TO* __restrict__ out, float* __restrict__ residual, const float* __restrict__ x,
+                                        int n_parts, size_t part_stride, const float* __restrict__ w,
+                                        const float* __restrict__ b, const int* __restrict__ rows, int width, float eps) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows != nullptr ? rows[r] : r;
+  const float* xr = x + (size_t)src * width;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = xr[c];
+    for (int p = 1; p < n_parts; ++p) v += xr[p * part_stride + c];
+    row[c] = v;
+    acc += v;
+  }
+  const float mean = block_sum(acc, scratch) / (float)width;
+  acc = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float d = row[c] - mean;
+    acc = fmaf(d, d, acc);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float y = ((row[c] - mean) * inv) * w[c] + (b != nullptr ? b[c] : 0.f);
+    if (residual != nullptr) residual[(size_t)r * width + c] += y;
+    else out[(size_t)r * width + c] = from_float<TO>(y);
+  }
+}
+
 }  // namespace xrt
+
+XRT_EXPORT int xrt_layernorm_affine(void* out, float* residual, const float* x, int n_parts, long long part_stride,
+                                    const float* weight, const float* bias, const int* rows, int n_rows, int width,
+                                    float eps, int out_dtype, cudaStream_t stream) {
+  if (n_rows < 0 || width <= 0 || n_parts < 1 || (out == nullptr) == (residual == nullptr)) return XRT_ERR_ARGUMENT;
+  if ((size_t)width * sizeof(float) > 160 * 1024) return XRT_ERR_UNSUPPORTED;
+  if (n_rows == 0) return XRT_OK;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+  const size_t smem = (size_t)width * sizeof(float);
+  XRT_DISPATCH_DTYPE(out_dtype, TO, {
+    auto kernel = xrt::layernorm_affine_kernel<TO>;
+    if (smem > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return (int)err;
+    }
+    xrt::launch_kernel(kernel, dim3(n_rows), dim3(threads), smem, stream, (TO*)out, residual, x, n_parts,
+                       (size_t)part_stride, weight, bias, rows, width, eps);
+  });
+  return xrt::launch_status();
+}
 
 
 XRT_EXPORT int xrt_layernorm(void* out, const float* x, const void* weight, const int* rows, int n_rows,

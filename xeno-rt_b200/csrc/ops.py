@@ -32,18 +32,27 @@ _SIGNATURES = {
     "xrt_swiglu": [_P, _P, _I, _I, _I, _I, _P],
     "xrt_rotation_table": [_P, _P, _P, _F, _I, _I, _P],
     "xrt_state_scan": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "xrt_short_conv": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_ssd_scan": [_P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "xrt_gated_group_norm": [_P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _P],
+    "xrt_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "xrt_moe_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+    "xrt_relu_squared": [_P, _P, _I, _I, _I, _P],
+    "xrt_embedding_pair": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "xrt_layernorm_affine": [_P, _P, _P, _I, ctypes.c_longlong, _P, _P, _P, _I, _I, _F, _I, _P],
+    "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I,
+                            _I, _I, _I, _I, _P],
     "xrt_decay": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
     "xrt_unit_heads": [_P, _I, _I, _I, _I, _F, _I, _F, _P],
     "xrt_head_norm_gate": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
-    "xrt_gate_mul": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "xrt_gate_mul": [_P, _P, _I, _I, _I, _I, _I, _I, _P],
     "xrt_rms_scale_add": [_P, _P, _P, _I, _I, _F, _F, _P],
     "xrt_concat_cast": [_P, _P, _P, _I, _I, _I, _P],
     "xrt_scale_softcap": [_P, _I, _I, _F, _F, _P],
     "xrt_rope_table": [_P, _P, _P, _F, _I, _I, _P],
     "xrt_qk_rope_kv_write": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                              _I, _I, _I, _I, _I, _P],
-    "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
+    "xrt_attention_reference": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _I, _I, _I, _P],
     "xrt_gemm_reference": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gemm_stream_norm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P, _P],
@@ -58,7 +67,7 @@ _SIGNATURES = {
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
     "xrt_attention_decode_qkv": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I,
                                  _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
-    "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _P],
     "xrt_attention_prefill_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
     "xrt_sample": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P],
@@ -314,8 +323,11 @@ def qk_rope_kv_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, q
 
 
 def attention_reference(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
-                        head_dim: int, scale: float, window: int = 0) -> None:
-    """Causal GQA attention over the cache, one warp per (token, head); any dtype."""
+                        head_dim: int, scale: float, window: int = 0, keep_first: int = 0, softcap: float = 0.0,
+                        distance_rate: float = 0.0) -> None:
+    """Causal GQA attention over the cache, one warp per (token, head); any dtype.  ``keep_first``: so many first
+    keys stay visible behind the window; ``softcap``: s <- cap tanh(s / cap); ``distance_rate`` r: head h's scores
+    lose 2^(-r (h + 1) / heads) for every position between query and key (each 0 = off)."""
     n = q.shape[0]
     if q.shape != (n, n_heads * head_dim) or out.shape != q.shape:
         raise KernelError("attention_reference: shapes do not fit")
@@ -325,7 +337,8 @@ def attention_reference(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, 
         _ptr(out, "out"), _ptr(q, "q"), _ptr(k_pool, "k_pool"), _ptr(v_pool, "v_pool", k_pool.dtype),
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), _code(q.dtype), _code(k_pool.dtype), _code(out.dtype), _stream()),
+        float(scale), int(window), int(keep_first), float(softcap), float(distance_rate), _code(q.dtype),
+        _code(k_pool.dtype), _code(out.dtype), _stream()),
         "attention_reference")
 
 
@@ -659,8 +672,10 @@ def attention_decode_fused_max_splits(head_dim: int, group: int) -> int:
 
 
 def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_new: int,
-                      n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """bfloat16 causal attention of sequences laid end to end, each continuing at seq_start."""
+                      n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0, keep_first: int = 0,
+                      softcap: float = 0.0, distance_rate: float = 0.0) -> None:
+    """bfloat16 causal attention of sequences laid end to end, each continuing at seq_start.  ``keep_first``,
+    ``softcap``, ``distance_rate``: the score options of ``attention_reference``."""
     n = q.shape[0]
     n_seqs = seq_slot.numel()
     if q.shape != (n, n_heads * head_dim) or out.shape != q.shape or cu_seqlens.numel() != n_seqs + 1:
@@ -672,7 +687,8 @@ def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, b
         _ptr(v_pool, "v_pool", torch.bfloat16), _ptr(cu_seqlens, "cu_seqlens", torch.int32),
         _ptr(seq_slot, "seq_slot", torch.int32), _ptr(seq_start, "seq_start", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n_seqs, int(max_new), n_heads,
-        n_kv_heads, head_dim, float(scale), int(window), _stream()), "attention_prefill")
+        n_kv_heads, head_dim, float(scale), int(window), int(keep_first), float(softcap), float(distance_rate),
+        _stream()), "attention_prefill")
 
 
 def attention_prefill_tcgen05(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_new: int,
@@ -772,8 +788,8 @@ def state_scan(out, q, k, v, decay, beta, state, cu_seqlens, seq_slot, n_heads: 
            "state_scan")
 
 
-def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: str = "silu") -> None:
-    """out[t, c] = act(sum_j weight[c, j] * x[t - (taps - 1) + j, c]) inside each sequence; inputs before the
+def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: str = "silu", bias=None) -> None:
+    """out[t, c] = act(bias[c] + sum_j weight[c, j] * x[t - (taps - 1) + j, c]) inside each sequence (no bias: 0); inputs before the
     step come from ``state`` [slots, taps - 1, channels] (zeros at a sequence's start), which is left holding
     the sequence's last taps - 1 inputs.  x: float32 rows of at least ``channels`` columns; all float32."""
     n, channels = out.shape
@@ -784,7 +800,10 @@ def short_conv(out, x, weight, state, cu_seqlens, seq_slot, max_new: int, act: s
         raise KernelError("short_conv: the state must be [slots, taps - 1, channels]")
     xp, xs = _columns(x, "x", channels)
     n_seqs = seq_slot.numel()
+    if bias is not None and bias.numel() != channels:
+        raise KernelError("short_conv: one bias a channel is needed")
     _check(_kernels().xrt_short_conv(_ptr(out, "out"), xp, xs, _ptr(weight, "weight", torch.float32),
+                                    _ptr(bias, "bias", torch.float32),
                                     _ptr(state if taps > 1 else None, "state", torch.float32),
                                     _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
                                     n_seqs, int(max_new), channels, taps, _ACTS[act], _stream()), "short_conv")
@@ -826,13 +845,16 @@ def head_norm_gate(y, o, weight, gate, n_heads: int, vdim: int, eps: float, act:
            "head_norm_gate")
 
 
-def gate_mul(x, gate, act: str = "sigmoid") -> None:
-    """x[t, c] *= act(gate[t, c]) in place; gate: float32 rows of at least x's width."""
-    gp, gs = _columns(gate, "gate", x.shape[1])
+def gate_mul(x, gate, act: str = "sigmoid", group: int = 1) -> None:
+    """x[t, c] *= act(gate[t, c // group]) in place; gate: float32 rows of at least x's width / group (``group``
+    columns share a gate: a head's, say)."""
+    if group < 1 or x.shape[1] % group:
+        raise KernelError("gate_mul: the width is no multiple of the group")
+    gp, gs = _columns(gate, "gate", x.shape[1] // group)
     if gate.shape[0] != x.shape[0]:
         raise KernelError("gate_mul: shapes do not fit")
-    _check(_kernels().xrt_gate_mul(_ptr(x, "x"), gp, gs, x.shape[0], x.shape[1], _ACTS[act], _code(x.dtype), _stream()),
-           "gate_mul")
+    _check(_kernels().xrt_gate_mul(_ptr(x, "x"), gp, gs, x.shape[0], x.shape[1], _ACTS[act], _code(x.dtype), int(group),
+                                  _stream()), "gate_mul")
 
 
 def rms_scale_add(residual, y, weight, eps: float, factor: float = 1.0) -> None:
@@ -856,3 +878,148 @@ def scale_softcap(x, scale: float, cap: float | None) -> None:
     """x <- cap * tanh(x * scale / cap) in place (x * scale without a cap); x float32 [rows, width]."""
     _check(_kernels().xrt_scale_softcap(_ptr(x, "x", torch.float32), x.shape[0], x.shape[1], float(scale),
                                        float(cap) if cap else 0.0, _stream()), "scale_softcap")
+
+
+# ---------------------------------------------------------------------------------------------------
+# The scalar-decay state-space scan and its group norm (csrc/ssd.cu), routed experts (csrc/moe.cu), and the small
+# steps of layers that norm a sublayer's result before adding it
+def ssd_scan(out, x, b, c, dt, dt_bias, a_log, d_skip, state, cu_seqlens, seq_slot, n_heads: int, n_groups: int,
+             n_state: int, vdim: int, max_new: int = 0) -> None:
+    """S <- exp(-exp(a_log) dt) S + dt b x^T, out = S^T c + d_skip x per head, dt = softplus(raw + dt_bias); x rows of
+    heads * vdim, b and c rows of groups * n_state (one stride), dt rows of one raw step a head (all float32, rows may
+    be slices of wider rows); ``state`` float32 [slots, heads, vdim, n_state] is read and left as the last state."""
+    n = out.shape[0]
+    if out.shape != (n, n_heads * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("ssd_scan: out must be float32 [T, heads * vdim]")
+    if state.dim() != 4 or tuple(state.shape[1:]) != (n_heads, vdim, n_state) or state.dtype != torch.float32:
+        raise KernelError("ssd_scan: the state must be float32 [slots, heads, vdim, n_state]")
+    xp, xs = _columns(x, "x", n_heads * vdim)
+    bp, bs = _columns(b, "b", n_groups * n_state)
+    cp, cs = _columns(c, "c", n_groups * n_state)
+    dp, ds = _columns(dt, "dt", n_heads)
+    if bs != cs or any(t.shape[0] != n for t in (x, b, c, dt)):
+        raise KernelError("ssd_scan: one row a token, and b and c rows of one stride, are needed")
+    for v in (dt_bias, a_log, d_skip):
+        if v.numel() != n_heads or v.dtype != torch.float32:
+            raise KernelError("ssd_scan: dt_bias, a_log and d_skip are float32 [heads]")
+    n_seqs = seq_slot.numel()
+    if cu_seqlens.numel() != n_seqs + 1:
+        raise KernelError("ssd_scan: cu_seqlens must hold one entry more than seq_slot")
+    _check(_kernels().xrt_ssd_scan(_ptr(out, "out"), xp, xs, bp, cp, bs, dp, ds, _ptr(dt_bias, "dt_bias"),
+                                  _ptr(a_log, "a_log"), _ptr(d_skip, "d_skip"), _ptr(state, "state"),
+                                  _ptr(cu_seqlens, "cu_seqlens", torch.int32), _ptr(seq_slot, "seq_slot", torch.int32),
+                                  n_seqs, n_heads, n_groups, n_state, vdim, int(max_new), _stream()), "ssd_scan")
+
+
+def gated_group_norm(out, y, z, weight, groups: int, eps: float) -> None:
+    """out = v / sqrt(mean(v^2 over the group) + eps) * weight with v = y * silu(z), each of ``groups`` equal stretches
+    of a row by itself; y float32 [T, width], z float32 rows of at least width, weight float32 [width]."""
+    n, width = y.shape
+    if out.shape != y.shape or y.dtype != torch.float32 or weight.numel() != width or weight.dtype != torch.float32:
+        raise KernelError("gated_group_norm: shapes do not fit")
+    zp, zs = _columns(z, "z", width)
+    _check(_kernels().xrt_gated_group_norm(_ptr(out, "out"), _ptr(y, "y"), zp, zs, _ptr(weight, "weight"), n, width,
+                                          int(groups), float(eps), _code(out.dtype), _stream()), "gated_group_norm")
+
+
+def moe_route(ids, weights, logits, bias, top: int) -> None:
+    """The ``top`` largest of logits + bias a row (ids int32 [T, top]) and the softmax over them (weights float32)."""
+    n, experts = logits.shape
+    if ids.shape != (n, top) or weights.shape != (n, top) or logits.dtype != torch.float32:
+        raise KernelError("moe_route: shapes do not fit")
+    _check(_kernels().xrt_moe_route(_ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32),
+                                   _ptr(logits, "logits"), _ptr(bias, "bias", torch.float32), n, experts, int(top),
+                                   _stream()), "moe_route")
+
+
+def moe_experts(out, h, w_in, w_out, ids, weights, ff: int, limit: float, alpha: float) -> None:
+    """out[c, t] = weights[t, c] * expert ids[t, c] of h[t]; out float32 [top, T, width]; w_in [experts * 2 * ff,
+    width] (an expert's gate rows, then its up rows), w_out [experts * width, ff]."""
+    top, n, width = out.shape
+    if h.shape != (n, width) or ids.shape != (n, top) or w_in.shape[1] != width or w_out.shape[1] != ff:
+        raise KernelError("moe_experts: shapes do not fit")
+    if w_in.shape[0] % (2 * ff) or w_out.shape[0] != w_in.shape[0] // (2 * ff) * width or out.dtype != torch.float32:
+        raise KernelError("moe_experts: the experts' matrices do not fit")
+    _check(_kernels().xrt_moe_experts(_ptr(out, "out"), _ptr(h, "h"), _ptr(w_in, "w_in"), _ptr(w_out, "w_out", w_in.dtype),
+                                     _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32), n, width,
+                                     int(ff), top, float(limit), float(alpha), _code(h.dtype), _code(w_in.dtype),
+                                     _stream()), "moe_experts")
+
+
+def relu_squared(out, x) -> None:
+    """out = max(x, 0)^2; x float32 [T, width]."""
+    if out.shape != x.shape or x.dtype != torch.float32:
+        raise KernelError("relu_squared: shapes do not fit")
+    _check(_kernels().xrt_relu_squared(_ptr(out, "out"), _ptr(x, "x"), x.shape[0], x.shape[1], _code(out.dtype),
+                                      _stream()), "relu_squared")
+
+
+def embedding_pair(out, table, pairs, ids, tok_slot, tok_pos, last_token, cu_seqlens, seq_slot, mul_prev: int,
+                   mul_cur: int, error_flag) -> None:
+    """out[t] = table[id] + pairs[(previous * mul_prev + id * mul_cur) mod buckets] (pairs' last row at position 0);
+    ``last_token`` int32 [slots] gives a step's first tokens their previous token and is left holding the last."""
+    n, hidden = out.shape
+    buckets = pairs.shape[0] - 1
+    if table.shape[1] != hidden or pairs.shape[1] != hidden or ids.numel() != n or pairs.dtype != table.dtype or buckets < 1:
+        raise KernelError("embedding_pair: shapes do not fit")
+    n_seqs = seq_slot.numel()
+    _check(_kernels().xrt_embedding_pair(_ptr(out, "out", torch.float32), _ptr(table, "table"), _ptr(pairs, "pairs"),
+                                        _ptr(ids, "ids", torch.int32), _ptr(tok_slot, "tok_slot", torch.int32),
+                                        _ptr(tok_pos, "tok_pos", torch.int32), _ptr(last_token, "last_token", torch.int32),
+                                        _ptr(cu_seqlens, "cu_seqlens", torch.int32),
+                                        _ptr(seq_slot, "seq_slot", torch.int32), n, n_seqs, hidden, table.shape[0], buckets,
+                                        int(mul_prev), int(mul_cur), _code(table.dtype),
+                                        _ptr(error_flag, "error_flag", torch.int32), _stream()), "embedding_pair")
+    add_launches(1)
+
+
+def layernorm_affine(x, weight, bias, eps: float, out=None, residual=None, rows=None, n_parts: int = 1) -> None:
+    """y = (x - mean) / sqrt(variance + eps) * weight + bias over float32 rows; written to ``out`` (any dtype), or
+    added into ``residual`` (float32) when that is given.  ``x`` may be [n_parts, T, width]: the parts are added in
+    index order first.  ``rows`` gathers rows of x."""
+    width = x.shape[-1]
+    target = out if out is not None else residual
+    if (out is None) == (residual is None) or target.shape[-1] != width or x.dtype != torch.float32:
+        raise KernelError("layernorm_affine: give out or residual, of x's width")
+    if x.dim() != (3 if n_parts > 1 else 2) or (n_parts > 1 and x.shape[0] != n_parts) or not x.is_contiguous():
+        raise KernelError("layernorm_affine: x must be [T, width] or [parts, T, width]")
+    n_rows = target.shape[0]
+    if rows is not None and rows.numel() != n_rows or rows is None and x.shape[-2] != n_rows:
+        raise KernelError("layernorm_affine: rows do not fit")
+    if weight.numel() != width or (bias is not None and bias.numel() != width):
+        raise KernelError("layernorm_affine: weight and bias must be [width]")
+    _check(_kernels().xrt_layernorm_affine(_ptr(out, "out"), _ptr(residual, "residual", torch.float32), _ptr(x, "x"),
+                                          int(n_parts), x.shape[-2] * width if n_parts > 1 else 0,
+                                          _ptr(weight, "weight", torch.float32), _ptr(bias, "bias", torch.float32),
+                                          _ptr(rows, "rows", torch.int32), n_rows, width, float(eps),
+                                          _code(out.dtype) if out is not None else 0, _stream()), "layernorm_affine")
+
+
+def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bias, unit_norm: bool, norm_dim: int,
+                    eps: float, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int,
+                    v_keep=None, v_first=None, v_blend: float = 0.0, write_kv: bool = True) -> None:
+    """``qk_rope_kv_write`` without rotation for layers that add a bias a column of the q/k/v row (float32, laid out as
+    the row), divide q and k heads by their root mean square without a weight (over ``norm_dim`` dims where the heads
+    are laid out wider), keep the values in 32-bit (``v_keep`` [T, kv heads * head_dim]) and / or cache
+    (1 - v_blend) v + v_blend v_first."""
+    n = qkv.shape[0]
+    if q_out.shape != (n, n_heads * head_dim) or tok_slot.numel() != n or tok_pos.numel() != n:
+        raise KernelError("qkv_heads_write: shapes do not fit")
+    if write_kv:
+        for pool in (k_pool, v_pool):
+            if pool.dim() != 4 or pool.shape[1] != n_kv_heads or pool.shape[2] != 64 or pool.shape[3] != head_dim:
+                raise KernelError("qkv_heads_write: the cache pool must be [blocks, kv heads, 64, head_dim]")
+        if qkv.shape[1] < v_offset + n_kv_heads * head_dim:
+            raise KernelError("qkv_heads_write: the q/k/v row is too short")
+    if bias is not None and bias.numel() < v_offset + n_kv_heads * head_dim:
+        raise KernelError("qkv_heads_write: the bias is shorter than the q/k/v row")
+    kp, ks = _columns(v_keep, "v_keep", n_kv_heads * head_dim) if v_keep is not None else (0, 0)
+    fp, fs = _columns(v_first, "v_first", n_kv_heads * head_dim) if v_first is not None else (0, 0)
+    cache_dtype = k_pool.dtype if write_kv else q_out.dtype
+    _check(_kernels().xrt_qkv_heads_write(
+        _ptr(q_out, "q_out"), _ptr(k_pool if write_kv else None, "k_pool"), _ptr(v_pool if write_kv else None, "v_pool"),
+        _ptr(qkv, "qkv", torch.float32), qkv.shape[1], k_offset, v_offset, _ptr(bias, "bias", torch.float32),
+        1 if unit_norm else 0, int(norm_dim), float(eps), kp, ks, fp, fs, float(v_blend),
+        _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
+        1 if write_kv else 0, _code(q_out.dtype), _code(cache_dtype), _stream()), "qkv_heads_write")

@@ -43,6 +43,23 @@ __global__ void rotation_table_kernel(float2* __restrict__ cos_sin, const int* _
   cos_sin[i] = make_float2(c * magnitude, s * magnitude);
 }
 
+// What a layer may ask for beside norm, rotation and the cache write (all optional, all 32-bit):
+//   bias       one float a column of the q/k/v row (laid out as the row is), added first
+//   unit_norm  q and k heads are divided by their root mean square, without a weight
+//   norm_dim   the divisor of the heads' mean of squares where the heads are laid out wider than they are (0: head_dim)
+//   v_keep     the values (after the bias) are also written here in 32-bit, [tokens, v_keep_stride]
+//   v_first    the cached value is (1 - v_blend) v + v_blend v_first[token], v_first rows of v_first_stride floats
+struct HeadExtras {
+  const float* bias = nullptr;
+  int unit_norm = 0;
+  int norm_dim = 0;
+  float* v_keep = nullptr;
+  int v_keep_stride = 0;
+  const float* v_first = nullptr;
+  int v_first_stride = 0;
+  float v_blend = 0.f;
+};
+
 // One warp per (token, head) among [q heads | k heads | v heads].  MAX_PER_LANE * 32 >= head_dim.
 template <typename TN, typename TQ, typename TC, int MAX_PER_LANE>
 __global__ void qk_rope_kv_write_kernel(
@@ -52,7 +69,7 @@ __global__ void qk_rope_kv_write_kernel(
     const float2* __restrict__ cos_sin, int rope_half,
     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
     const int* __restrict__ block_table, int max_blocks,
-    int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved) {
+    int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved, const HeadExtras ex) {
   extern __shared__ float staged[];  // [warps][head_dim]
   pdl_trigger();
   pdl_wait();
@@ -77,23 +94,40 @@ __global__ void qk_rope_kv_write_kernel(
     return;
   }
 
-  const float* src = qkv + (size_t)t * row_stride +
-                     (kind == 0 ? 0 : (kind == 1 ? k_offset : v_offset)) + head * head_dim;
+  const int column = (kind == 0 ? 0 : (kind == 1 ? k_offset : v_offset)) + head * head_dim;
+  const float* src = qkv + (size_t)t * row_stride + column;
   float v[MAX_PER_LANE];
   float sq = 0.f;
 #pragma unroll
   for (int j = 0; j < MAX_PER_LANE; ++j) {
     const int d = lane + 32 * j;
     v[j] = d < head_dim ? src[d] : 0.f;
+    if (ex.bias != nullptr && d < head_dim) v[j] += ex.bias[column + d];
     sq = fmaf(v[j], v[j], sq);
   }
   const TN* norm_w = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+  const float norm_dim = (float)(ex.norm_dim > 0 ? ex.norm_dim : head_dim);
   if (norm_w != nullptr) {
-    const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)head_dim + eps);
+    const float inv = 1.0f / sqrtf(warp_sum(sq) / norm_dim + eps);
 #pragma unroll
     for (int j = 0; j < MAX_PER_LANE; ++j) {
       const int d = lane + 32 * j;
       if (d < head_dim) v[j] = (v[j] * inv) * to_float(norm_w[d]);
+    }
+  } else if (ex.unit_norm && kind != 2) {
+    const float inv = 1.0f / sqrtf(warp_sum(sq) / norm_dim + eps);
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) v[j] *= inv;
+  }
+  if (kind == 2) {
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+      const int d = lane + 32 * j;
+      if (d < head_dim) {
+        if (ex.v_keep != nullptr) ex.v_keep[(size_t)t * ex.v_keep_stride + head * head_dim + d] = v[j];
+        if (ex.v_first != nullptr)
+          v[j] = (1.0f - ex.v_blend) * v[j] + ex.v_blend * ex.v_first[(size_t)t * ex.v_first_stride + head * head_dim + d];
+      }
     }
   }
 
@@ -279,17 +313,18 @@ XRT_EXPORT int xrt_rotation_table(float* cos_sin, const int* pos, const float* f
 // q_out: [n_tokens, n_heads * head_dim] in q_dtype.  k_pool / v_pool: the cache blocks of this
 // layer, [n_blocks, n_kv_heads, 64, head_dim] in cache_dtype.  Norm weights may be null (no head
 // norm) and share norm_dtype.  write_kv = 0 leaves the cache alone (a layer reading another's).
-XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, const float* qkv, int row_stride,
-                                    int k_offset, int v_offset, const void* q_norm_w, const void* k_norm_w,
-                                    float eps, const float* cos_sin, int rope_half, const int* tok_slot,
-                                    const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
-                                    int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved,
-                                    int norm_dtype, int q_dtype, int cache_dtype, cudaStream_t stream) {
+static int qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, const float* qkv, int row_stride,
+                            int k_offset, int v_offset, const void* q_norm_w, const void* k_norm_w,
+                            float eps, const float* cos_sin, int rope_half, const int* tok_slot,
+                            const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
+                            int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved,
+                            int norm_dtype, int q_dtype, int cache_dtype, const xrt::HeadExtras& ex, cudaStream_t stream) {
+  const bool plain = ex.bias == nullptr && !ex.unit_norm && ex.norm_dim == 0 && ex.v_keep == nullptr && ex.v_first == nullptr;
   if (n_tokens < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return XRT_ERR_ARGUMENT;
   if (head_dim > 256 || 2 * rope_half > head_dim) return XRT_ERR_UNSUPPORTED;
   if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
-  const bool fast = head_dim == 128 && (rope_half == 0 || (rope_half == 64 && !interleaved)) && row_stride % 4 == 0 && k_offset % 4 == 0 &&
+  const bool fast = plain && head_dim == 128 && (rope_half == 0 || (rope_half == 64 && !interleaved)) && row_stride % 4 == 0 && k_offset % 4 == 0 &&
                     v_offset % 4 == 0 &&
                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)cos_sin) & 15) == 0;
   if (fast) {
@@ -315,9 +350,42 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
         xrt::launch_kernel(xrt::qk_rope_kv_write_kernel<TN, TQ, TC, 8>, grid, dim3(warps * 32), smem, stream,
             (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, qkv, row_stride, k_offset, v_offset, (const TN*)q_norm_w,
             (const TN*)k_norm_w, eps, (const float2*)cos_sin, rope_half, tok_slot, tok_pos, block_table,
-            max_blocks, n_heads, n_kv_heads, head_dim, write_kv, interleaved);
+            max_blocks, n_heads, n_kv_heads, head_dim, write_kv, interleaved, ex);
       });
     });
   });
   return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, const float* qkv, int row_stride,
+                                    int k_offset, int v_offset, const void* q_norm_w, const void* k_norm_w,
+                                    float eps, const float* cos_sin, int rope_half, const int* tok_slot,
+                                    const int* tok_pos, const int* block_table, int max_blocks, int n_tokens,
+                                    int n_heads, int n_kv_heads, int head_dim, int write_kv, int interleaved,
+                                    int norm_dtype, int q_dtype, int cache_dtype, cudaStream_t stream) {
+  return qk_rope_kv_write(q_out, k_pool, v_pool, qkv, row_stride, k_offset, v_offset, q_norm_w, k_norm_w, eps, cos_sin,
+                          rope_half, tok_slot, tok_pos, block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim,
+                          write_kv, interleaved, norm_dtype, q_dtype, cache_dtype, xrt::HeadExtras(), stream);
+}
+
+// The same with a bias a column, weightless unit norms of q and k, and values that are kept in 32-bit and / or
+// blended with another layer's values of the same tokens before they are cached (see HeadExtras).
+XRT_EXPORT int xrt_qkv_heads_write(void* q_out, void* k_pool, void* v_pool, const float* qkv, int row_stride,
+                                   int k_offset, int v_offset, const float* bias, int unit_norm, int norm_dim, float eps,
+                                   float* v_keep, int v_keep_stride, const float* v_first, int v_first_stride,
+                                   float v_blend, const int* tok_slot, const int* tok_pos, const int* block_table,
+                                   int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv,
+                                   int q_dtype, int cache_dtype, cudaStream_t stream) {
+  xrt::HeadExtras ex;
+  ex.bias = bias;
+  ex.unit_norm = unit_norm;
+  ex.norm_dim = norm_dim;
+  ex.v_keep = v_keep;
+  ex.v_keep_stride = v_keep_stride;
+  ex.v_first = v_first;
+  ex.v_first_stride = v_first_stride;
+  ex.v_blend = v_blend;
+  return qk_rope_kv_write(q_out, k_pool, v_pool, qkv, row_stride, k_offset, v_offset, nullptr, nullptr, eps, nullptr, 0,
+                          tok_slot, tok_pos, block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, write_kv,
+                          0, XRT_F32, q_dtype, cache_dtype, ex, stream);
 }

@@ -5,7 +5,7 @@
 //   state scan        S_t = diag(a_t) S_(t-1) + k_t u_t^T,   o_t = S_t^T q_t
 //                     plain:       u_t = v_t                                   (gated linear attention)
 //                     delta rule:  u_t = b_t (v_t - (diag(a_t) S_(t-1))^T k_t) (the read-out sees the write)
-//   short convolution y_t = act(sum_j w[c, j] x_(t - (taps - 1) + j)) per channel, zeros before a sequence's
+//   short convolution y_t = act(bias[c] + sum_j w[c, j] x_(t - (taps - 1) + j)) per channel (the bias is optional), zeros before a sequence's
 //                     start; the last taps - 1 inputs of a sequence are its state
 //   decays            a = sigmoid(z + bias)^(1 / tau)   or   a = exp(-exp(A) softplus(z + bias))
 //   unit heads        x / sqrt(sum(x^2) + eps) * scale per head
@@ -244,7 +244,8 @@ __global__ void __launch_bounds__(128) state_scan_kernel(const ScanArgs a) {
 // grid (sequences, token tiles, channel blocks); a thread has one channel of a tile's tokens.  Inputs before the step's first token
 // come from the sequence's state [slot][taps - 1][channels] (the newest last).
 __global__ void short_conv_kernel(float* __restrict__ out, const float* __restrict__ x, int x_stride,
-                                  const float* __restrict__ w, const float* __restrict__ state,
+                                  const float* __restrict__ w, const float* __restrict__ bias,
+                                  const float* __restrict__ state,
                                   const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int channels,
                                   int taps, int tile_tokens, int act) {
   pdl_trigger();
@@ -258,7 +259,7 @@ __global__ void short_conv_kernel(float* __restrict__ out, const float* __restri
   const float* st = state + (size_t)slot * (taps - 1) * channels;
   for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < channels; c += gridDim.z * blockDim.x) {
     for (int l = l0; l < l1; ++l) {
-      float acc = 0.f;
+      float acc = bias != nullptr ? bias[c] : 0.f;
       for (int jj = 0; jj < taps; ++jj) {
         const int src = l - (taps - 1) + jj;  // local index of the input under tap jj
         const float xv = src >= 0 ? x[(size_t)(begin + src) * x_stride + c] : st[(size_t)(taps - 1 + src) * channels + c];
@@ -350,13 +351,13 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ y, const float* __restric
 // x[t, c] *= act(gate[t, c]) in place.
 template <typename TX>
 __global__ void gate_mul_kernel(TX* __restrict__ x, const float* __restrict__ gate, int gate_stride, int n_tokens,
-                                int width, int act) {
+                                int width, int act, int group) {
   pdl_trigger();
   pdl_wait();
   const size_t total = (size_t)n_tokens * width;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / width, c = i - t * width;
-    x[i] = from_float<TX>(to_float(x[i]) * activate(gate[t * gate_stride + c], act));
+    x[i] = from_float<TX>(to_float(x[i]) * activate(gate[t * gate_stride + c / group], act));  // one gate a group of columns
   }
 }
 
@@ -487,7 +488,7 @@ XRT_EXPORT int xrt_state_scan(float* out, const float* q, int q_stride, const fl
   return xrt::launch_status();
 }
 
-XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const float* w, float* state,
+XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const float* w, const float* bias, float* state,
                               const int* cu_seqlens, const int* seq_slot, int n_seqs, int max_new, int channels,
                               int taps, int act, cudaStream_t stream) {
   if (n_seqs < 0 || channels <= 0 || taps < 1 || max_new < 0) return XRT_ERR_ARGUMENT;
@@ -498,7 +499,7 @@ XRT_EXPORT int xrt_short_conv(float* out, const float* x, int x_stride, const fl
   const int channel_blocks = (channels + threads - 1) / threads;
   xrt::launch_kernel(xrt::short_conv_kernel,
                      dim3(n_seqs, (max_new + tile_tokens - 1) / tile_tokens, channel_blocks < 65535 ? channel_blocks : 65535),
-                     dim3(threads), 0, stream, out, x, x_stride, w, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
+                     dim3(threads), 0, stream, out, x, x_stride, w, bias, (const float*)state, cu_seqlens, seq_slot, channels, taps, tile_tokens,
                      act);
   if (taps > 1)
     xrt::launch_kernel(xrt::short_conv_state_kernel<8>, dim3(n_seqs, (channels + 255) / 256), dim3(256), 0, stream, state,
@@ -541,12 +542,12 @@ XRT_EXPORT int xrt_head_norm_gate(void* y, const float* o, const float* w, const
 }
 
 XRT_EXPORT int xrt_gate_mul(void* x, const float* gate, int gate_stride, int n_tokens, int width, int act, int dtype,
-                            cudaStream_t stream) {
-  if (n_tokens < 0 || width <= 0 || gate_stride < width) return XRT_ERR_ARGUMENT;
+                            int group, cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0 || group <= 0 || width % group || gate_stride < width / group) return XRT_ERR_ARGUMENT;
   if (n_tokens == 0) return XRT_OK;
   XRT_DISPATCH_DTYPE(dtype, TX, {
     xrt::launch_kernel(xrt::gate_mul_kernel<TX>, dim3(xrt::grid_for((size_t)n_tokens * width, 256)), dim3(256), 0, stream,
-                       (TX*)x, gate, gate_stride, n_tokens, width, act);
+                       (TX*)x, gate, gate_stride, n_tokens, width, act, group);
   });
   return xrt::launch_status();
 }

@@ -142,7 +142,12 @@ class Model:
         return needs
 
     def new_cache(self, max_tokens: int, max_slots: int | None = None) -> Cache:
-        return Cache(self.cache_needs(), max_tokens, self.max_positions, self.dtype, self.device, max_slots)
+        cache = Cache(self.cache_needs(), max_tokens, self.max_positions, self.dtype, self.device, max_slots)
+        ask = getattr(self.embedding, "state_need", None)
+        if ask is not None:  # an embedding that keeps something for every sequence (its previous token, say)
+            shape, dtype = ask()
+            cache.register_sequence_state("embedding", shape, dtype)
+        return cache
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx, cache: Cache, want_rows: torch.Tensor | None):
@@ -150,7 +155,11 @@ class Model:
         logits [len(want_rows), vocab] (None if no row is wanted).  The order inside is that of
         crates/xrt-models/src/llama.rs:432-613; the final norm and the output matrix see only the
         wanted rows (llama.rs:814-819 does so for the last token)."""
-        x = x0 = self.embedding.forward(ctx.token_ids, self.error_flag)
+        if hasattr(self.embedding, "state_need"):
+            x = x0 = self.embedding.forward(ctx.token_ids, self.error_flag, ctx=ctx,
+                                            state=cache.sequence_state["embedding"])
+        else:
+            x = x0 = self.embedding.forward(ctx.token_ids, self.error_flag)
         if self.stream_parts and self.spec.schedule[0].before is None:
             x = x0.clone()  # layers change x in place before the first stream part reads what the embedding gave
         for i, place in enumerate(self.spec.schedule):

@@ -2,5 +2,6 @@
 ``ModelSpec``, and registers both under the architecture's name."""
 from . import llama  # registers LlamaForCausalLM and Qwen3ForCausalLM
 from . import givopel  # registers Givopel
+from . import guzuvik  # registers Guzuvik
 
-__all__ = ["llama", "givopel"]
+__all__ = ["llama", "givopel", "guzuvik"]

@@ -44,7 +44,12 @@ class GroupedQueryAttention:
     dict ``{"kind", "params"}``); optional: ``v_head_dim`` (the value size of a head, default
     head_dim), ``scale`` (of the scores, default 1 / sqrt(head_dim)), ``gate`` ("sigmoid" or "silu":
     the concatenated heads are multiplied by that function of a product ``g`` of the mixer's input
-    before the output product).
+    before the output product; "sigmoid_head": one sigmoid gate a head, ``g`` [n_heads, width]), ``bias`` (q, k and v
+    have biases ``q_bias``, ``k_bias``, ``v_bias``), ``qk_norm`` = "unit" (q and k heads divided by their root mean
+    square, no weight), ``softcap`` (scores <- cap * tanh(scores / cap)), ``distance_rate`` r (head h's scores lose
+    2^(-r (h + 1) / n_heads) for every position between query and key), ``keep_first`` (so many first keys of a
+    sequence stay visible behind the window), ``value_blend`` (a name: the first layer of a model that gives this name
+    keeps its values of the step's tokens, every later one caches (1 - b) v + b v_first with its own scalar ``blend``).
     weights: ``q`` [n_heads*head_dim, width], ``k`` [n_kv_heads*head_dim, width], ``v``
     [n_kv_heads*v_head_dim, width], ``o`` [width, n_heads*v_head_dim], with qk_norm ``q_norm``,
     ``k_norm`` [head_dim], with a gate ``g`` [n_heads*v_head_dim, width].
@@ -70,17 +75,26 @@ class GroupedQueryAttention:
             return {}  # the part lays the heads out itself
         return {"qkvg": ("q", "k", "v", "g")} if params.get("gate") else {"qkv": ("q", "k", "v")}
 
+    @staticmethod
+    def _unit_norm(params) -> bool:
+        return params.get("qk_norm") == "unit"
+
     @classmethod
     def weight_shapes(cls, params):
         d, nh, nkv = params["width"], params["n_heads"], params["n_kv_heads"]
         hd, vd, _ = cls._sizes(params)
         shapes = {"q": ((nh * hd, d), "matrix"), "k": ((nkv * hd, d), "matrix"), "v": ((nkv * vd, d), "matrix"),
                   "o": ((d, nh * vd), "matrix")}
-        if params.get("qk_norm"):
+        if params.get("qk_norm") and not cls._unit_norm(params):
             shapes["q_norm"] = ((hd,), "vector")
             shapes["k_norm"] = ((hd,), "vector")
         if params.get("gate"):
-            shapes["g"] = ((nh * vd, d), "matrix")
+            shapes["g"] = ((nh if params["gate"] == "sigmoid_head" else nh * vd, d), "matrix")
+        if params.get("bias"):
+            shapes.update({"q_bias": ((nh * hd,), "vector"), "k_bias": ((nkv * hd,), "vector"),
+                           "v_bias": ((nkv * vd,), "vector")})
+        if params.get("value_blend"):
+            shapes["blend"] = ((), "vector")
         return shapes
 
     def __init__(self, params, weights, dtype: DType, device):
@@ -91,13 +105,19 @@ class GroupedQueryAttention:
         self.eps = float(params.get("eps", 1e-5))
         self.window = params.get("window")
         self.gate = params.get("gate")
-        if self.gate not in (None, "sigmoid", "silu"):
-            raise ConfigError(f"attention gate {self.gate!r} is not sigmoid or silu")
+        if self.gate not in (None, "sigmoid", "silu", "sigmoid_head"):
+            raise ConfigError(f"attention gate {self.gate!r} is not sigmoid, silu or sigmoid_head")
+        self.unit_norm = self._unit_norm(params)
+        self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
+        self.softcap = float(params.get("softcap") or 0.0)
+        self.distance_rate = float(params.get("distance_rate") or 0.0)
+        self.value_blend = params.get("value_blend")
+        self.true_dim = true_dim
         if self.n_heads % self.n_kv_heads:
             raise ConfigError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
         if not (16 <= self.head_dim <= 256):
             raise Unsupported(f"head size {max(true_dim, true_vdim)}: the attention kernels take head sizes up to 256")
-        if params.get("qk_norm") and true_dim != self.head_dim:
+        if params.get("qk_norm") and not self.unit_norm and true_dim != self.head_dim:
             raise Unsupported(f"q/k head norms with a head size of {true_dim} (no multiple of 16, or smaller than "
                               f"the value size) are not supported")
         self.q_width = self.n_heads * self.head_dim
@@ -109,18 +129,36 @@ class GroupedQueryAttention:
             pieces = [_pad_rows(weights["q"], self.n_heads, true_dim, self.head_dim),
                       _pad_rows(weights["k"], self.n_kv_heads, true_dim, self.head_dim),
                       _pad_rows(weights["v"], self.n_kv_heads, true_vdim, self.head_dim)]
-            if self.gate:
+            if self.gate == "sigmoid_head":
+                pieces.append(weights["g"])
+            elif self.gate:
                 pieces.append(_pad_rows(weights["g"], self.n_heads, true_vdim, self.head_dim))
             self.w_qkv = torch.cat(pieces, dim=0).contiguous()
             if true_vdim != self.head_dim:
                 self.w_o = _pad_columns(weights["o"], self.n_heads, true_vdim, self.head_dim)
         self.w_q = self.w_qkv[: self.q_width]
         self.gate_offset = self.q_width + 2 * self.kv_width
-        self.q_norm = weights.get("q_norm") if params.get("qk_norm") else None
-        self.k_norm = weights.get("k_norm") if params.get("qk_norm") else None
+        weighted = params.get("qk_norm") and not self.unit_norm
+        self.q_norm = weights.get("q_norm") if weighted else None
+        self.k_norm = weights.get("k_norm") if weighted else None
+        # one 32-bit bias a column of the q/k/v product's row, laid out as the row is (nothing for the gate's columns)
+        self.bias = None
+        if params.get("bias"):
+            def as_row(t, heads, size):
+                return _pad_rows(t.to(torch.float32).reshape(-1, 1), heads, size, self.head_dim).reshape(-1)
+            self.bias = torch.cat([as_row(weights["q_bias"], self.n_heads, true_dim),
+                                   as_row(weights["k_bias"], self.n_kv_heads, true_dim),
+                                   as_row(weights["v_bias"], self.n_kv_heads, true_vdim)]).contiguous()
+        self.blend = float(weights["blend"].to(torch.float32).reshape(-1)[0]) if self.value_blend else 0.0
+        # what the rotation kernel and the kernels that fold it in do not do: these layers prepare their heads with
+        # ops.qkv_heads_write and attend with the kernels that take the score options
+        self.plain_heads = self.bias is None and not self.unit_norm and not self.value_blend and true_dim == self.head_dim
+        self.plain_scores = not (self.keep_first or self.softcap or self.distance_rate)
         position = params.get("position") or {"kind": "none", "params": {}}
         self.position = part_class("position", position["kind"])(position.get("params", {}), {}, dtype, device)
         rope_dim = getattr(self.position, "rope_dim", 0)
+        if rope_dim and (self.bias is not None or self.unit_norm or self.value_blend):
+            raise Unsupported("a rotation together with biases, unit head norms or blended values is not supported")
         if rope_dim > true_dim:
             raise ConfigError(f"rope_dim {rope_dim} exceeds the head size {true_dim}")
         self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0 / math.sqrt(true_dim)
@@ -128,7 +166,7 @@ class GroupedQueryAttention:
         self.act_dtype = torch_dtype(dtype)
 
     def cache_need(self):
-        return KVNeed(self.n_kv_heads, self.head_dim, self.window)
+        return KVNeed(self.n_kv_heads, self.head_dim, self.window, self.keep_first)
 
     def takes_pending_norm(self, rows: int, device) -> bool:
         """Whether the first product of ``forward`` can finish a norm that the part before prepared."""
@@ -163,7 +201,7 @@ class GroupedQueryAttention:
         # padding rows belong to no sequence: kernels that walk sequences leave them unwritten
         padded = sum(ctx.new_lens) < ctx.n_tokens
         attended = (torch.zeros if padded else torch.empty)((n, self.q_width), dtype=self.act_dtype, device=h.device)
-        if self.dtype is DType.BF16:
+        if self.dtype is DType.BF16 and self.plain_heads and self.plain_scores:
             from . import attention_bf16
             if attention_bf16.decode_from_qkv(attended, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
                                               self.k_norm, self.eps, cos_sin, pairing, ctx, store, self.n_heads,
@@ -171,23 +209,39 @@ class GroupedQueryAttention:
                 qkv = None
         if qkv is not None:
             q = torch.empty((n, self.q_width), dtype=self.act_dtype, device=h.device)
-            ops.qk_rope_kv_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
-                                 self.k_norm, self.eps, cos_sin, ctx.tok_slot, ctx.tok_pos, store.block_table,
-                                 self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache, pairing=pairing)
+            if self.plain_heads:
+                ops.qk_rope_kv_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.q_norm,
+                                     self.k_norm, self.eps, cos_sin, ctx.tok_slot, ctx.tok_pos, store.block_table,
+                                     self.n_heads, self.n_kv_heads, self.head_dim, write_kv=owns_cache, pairing=pairing)
+            else:
+                v_keep = v_first = None
+                if self.value_blend and owns_cache:
+                    v_first = ctx.shared.get(("value_blend", self.value_blend))
+                    if v_first is None:  # the first layer of this name in the step: its values are the ones blended in
+                        v_keep = torch.zeros((n, self.kv_width), dtype=torch.float32, device=h.device)
+                        ctx.shared[("value_blend", self.value_blend)] = v_keep
+                ops.qkv_heads_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.bias,
+                                    self.unit_norm, self.true_dim, self.eps, ctx.tok_slot, ctx.tok_pos, store.block_table,
+                                    self.n_heads, self.n_kv_heads, self.head_dim, v_keep=v_keep, v_first=v_first,
+                                    v_blend=self.blend if v_first is not None else 0.0, write_kv=owns_cache)
             self.attend(attended, q, ctx, store)
-        if gated:
+        if self.gate == "sigmoid_head":
+            ops.gate_mul(attended, projected[:, self.gate_offset:], "sigmoid", group=self.head_dim)
+        elif gated:
             ops.gate_mul(attended, projected[:, self.gate_offset:], self.gate)
         return attended
 
     def attend(self, out, q, ctx, store):
         window = int(self.window) if self.window else 0
+        options = {} if self.plain_scores else {"keep_first": self.keep_first, "softcap": self.softcap,
+                                                "distance_rate": self.distance_rate}
         if self.dtype is DType.BF16:
             from . import attention_bf16
             if attention_bf16.run(out, q, ctx, store, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
-                                  window):
+                                  window, **options):
                 return
         ops.attention_reference(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table,
-                                self.n_heads, self.n_kv_heads, self.head_dim, self.scale, window)
+                                self.n_heads, self.n_kv_heads, self.head_dim, self.scale, window, **options)
 
 
 register_part("mixer", "attention", GroupedQueryAttention)

@@ -89,9 +89,18 @@ def decode_from_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, 
     return True
 
 
-def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window) -> bool:
+def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window, keep_first=0, softcap=0.0,
+        distance_rate=0.0) -> bool:
     if n_heads // n_kv_heads > 16:
         return False
+    scored = bool(keep_first or softcap or distance_rate)  # the layer's score options: kernels that take them only
+    if scored:
+        if ctx.all_single or head_dim % 16 or ctx.n_seqs > 65535 or n_heads > 65535:
+            return False
+        ops.attention_prefill(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
+                              store.block_table, ctx.max_new, n_heads, n_kv_heads, head_dim, scale, window,
+                              keep_first, softcap, distance_rate)
+        return True
     if ctx.all_single and ctx.n_tokens <= 65535:
         chunk, n_splits, clusters = _decode_split_of(ctx, n_kv_heads, q.device, window)
         # few sequences: the last block of a (token, kv head) merges its splits (one launch less);

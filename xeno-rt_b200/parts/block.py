@@ -70,7 +70,23 @@ def parallel_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> No
         ctx.then_norm = ctx.pending = None
 
 
+def sandwich_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> None:
+    """x += post_norm(mixer(norm(x))); x += post_norm(feed_forward(norm(x))): a norm before and after each sublayer.
+    The layer's parts are ``mixer_norm``, ``mixer``, ``mixer_post`` and, if it has a feed-forward, ``ffn_norm``,
+    ``ffn``, ``ffn_post``.  The mixer hands its result back (``mix``), the feed-forward too (``apply``: [T, width] or
+    [parts, T, width] float32), and the norm after it adds into the 32-bit stream (``add_into``)."""
+    ctx.then_norm = ctx.pending = None
+    h = parts.mixer_norm.forward(x)
+    parts.mixer_post.add_into(x, parts.mixer.mix(h, ctx, stores.get("mixer"), owns_cache))
+    ctx.then_norm = ctx.pending = None
+    if "ffn" in parts:
+        h = parts.ffn_norm.forward(x)
+        parts.ffn_post.add_into(x, parts.ffn.apply(h, ctx))
+        ctx.then_norm = ctx.pending = None
+
+
 register_part("arrangement", "parallel_residual", parallel_residual)
+register_part("arrangement", "sandwich_residual", sandwich_residual)
 
 
 # what a layer of this arrangement begins with: the norm it applies to the residual stream first, and the

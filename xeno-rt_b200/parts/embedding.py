@@ -29,6 +29,37 @@ class TokenEmbedding:
         return out
 
 
+class TokenPairEmbedding:
+    """x = E[token] + P[(previous token * mul_prev + token * mul_cur) mod buckets]; a sequence's first token takes P's
+    last row (number ``buckets``).  The previous token is state of the sequence (``state_need``): one int32 a slot,
+    read by a step's first tokens and left holding the step's last.
+    params: ``vocab_size``, ``width``, ``buckets``, ``mul_prev``, ``mul_cur``.
+    weights: ``weight`` [vocab, width], ``pairs`` [buckets + 1, width]."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_shapes(cls, params):
+        return {"weight": ((params["vocab_size"], params["width"]), "matrix"),
+                "pairs": ((params["buckets"] + 1, params["width"]), "matrix")}
+
+    def __init__(self, params, weights, dtype, device):
+        self.vocab_size = int(params["vocab_size"])
+        self.width = int(params["width"])
+        self.mul_prev, self.mul_cur = int(params["mul_prev"]), int(params["mul_cur"])
+        self.weight, self.pairs = weights["weight"], weights["pairs"]
+
+    def state_need(self):
+        """(shape, dtype) of what the part keeps for every sequence."""
+        return (), torch.int32
+
+    def forward(self, token_ids, error_flag, ctx=None, state=None):
+        out = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
+        ops.embedding_pair(out, self.weight, self.pairs, token_ids, ctx.tok_slot, ctx.tok_pos, state, ctx.cu_seqlens,
+                           ctx.seq_slot, self.mul_prev, self.mul_cur, error_flag)
+        return out
+
+
 class OutputHead:
     """logits = W . normed, no scaling or cap (crates/xrt-models/src/llama.rs:604-613); W is the
     embedding when the model ties them (llama.rs:301-305), which the spec expresses by giving both
@@ -55,4 +86,5 @@ class OutputHead:
 
 
 register_part("embedding", "token", TokenEmbedding)
+register_part("embedding", "token_pair", TokenPairEmbedding)
 register_part("lm_head", "linear", OutputHead)

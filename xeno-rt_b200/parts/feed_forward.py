@@ -1,5 +1,6 @@
-"""SwiGLU feed-forward: down( silu(gate(h)) * up(h) ), added to the residual
-(crates/xrt-models/src/llama.rs:584-601; crates/xrt-kernels/src/cpu/silu.rs:1-3, 22-24)."""
+"""Feed-forwards.  SwiGLU: down( silu(gate(h)) * up(h) ), added to the residual
+(crates/xrt-models/src/llama.rs:584-601; crates/xrt-kernels/src/cpu/silu.rs:1-3, 22-24).  Beside it a feed-forward
+without a gate, down( relu(up(h))^2 ), and a mixture of small gated experts of which every token uses a few."""
 from __future__ import annotations
 
 import torch
@@ -59,4 +60,97 @@ class SwiGLUFeedForward:
             linear(act, self.w_down, accumulate_into=residual)
 
 
+class SquaredReluFeedForward:
+    """down( relu(up(h))^2 ).  params: ``width``, ``inner``.  weights: ``up`` [inner, width], ``down`` [width, inner]."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_shapes(cls, params):
+        d, f = params["width"], params["inner"]
+        return {"up": ((f, d), "matrix"), "down": ((d, f), "matrix")}
+
+    def __init__(self, params, weights, dtype: DType, device):
+        self.inner = int(params["inner"])
+        self.w_up, self.w_down = weights["up"], weights["down"]
+        self.act_dtype = torch_dtype(dtype)
+
+    def _act(self, h):
+        act = torch.empty((h.shape[0], self.inner), dtype=self.act_dtype, device=h.device)
+        ops.relu_squared(act, linear(h, self.w_up, out_dtype=torch.float32))
+        return act
+
+    def apply(self, h, ctx):
+        """The result handed back, float32 [T, width]."""
+        return linear(self._act(h), self.w_down, out_dtype=torch.float32)
+
+    def forward(self, h, residual, ctx):
+        ctx.then_norm = None
+        linear(self._act(h), self.w_down, accumulate_into=residual)
+
+
+class RoutedExperts:
+    """``experts`` small gated feed-forwards of which a token uses the ``top`` with the largest router logits
+    z = W_router h + b (32-bit), weighted by the softmax over those logits alone.  An expert:
+    g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha g) * (u + 1), W_down y.
+    params: ``width``, ``inner`` (an expert's), ``experts``, ``top``, ``limit``, ``alpha``.
+    weights: ``router`` [experts, width], ``router_bias`` [experts], and for expert i ``gate<i>``, ``up<i>``
+    [inner, width], ``down<i>`` [width, inner]; they are kept as two buffers, [experts * 2 * inner, width] (an expert's
+    gate rows, then its up rows) and [experts * width, inner]."""
+
+    graph_safe = True
+
+    @classmethod
+    def fused_weights(cls, params):
+        n = int(params["experts"])
+        return {"experts_in": tuple(r for i in range(n) for r in (f"gate{i}", f"up{i}")),
+                "experts_out": tuple(f"down{i}" for i in range(n))}
+
+    @classmethod
+    def weight_shapes(cls, params):
+        d, f, n = params["width"], params["inner"], int(params["experts"])
+        shapes = {"router": ((n, d), "matrix"), "router_bias": ((n,), "vector")}
+        for i in range(n):
+            shapes.update({f"gate{i}": ((f, d), "matrix"), f"up{i}": ((f, d), "matrix"), f"down{i}": ((d, f), "matrix")})
+        return shapes
+
+    def __init__(self, params, weights, dtype: DType, device):
+        self.width, self.inner = int(params["width"]), int(params["inner"])
+        self.experts, self.top = int(params["experts"]), int(params["top"])
+        self.limit, self.alpha = float(params["limit"]), float(params["alpha"])
+        self.w_router = weights["router"]
+        self.router_bias = weights["router_bias"].to(torch.float32).contiguous()
+        fused = self.fused_weights(params)
+        self.w_in = weights.get("experts_in")
+        if self.w_in is None:
+            self.w_in = torch.cat([weights[r] for r in fused["experts_in"]], dim=0).contiguous()
+        self.w_out = weights.get("experts_out")
+        if self.w_out is None:
+            self.w_out = torch.cat([weights[r] for r in fused["experts_out"]], dim=0).contiguous()
+
+    def route(self, h):
+        """(expert numbers int32 [T, top], weights float32 [T, top])."""
+        n = h.shape[0]
+        logits = linear(h, self.w_router, out_dtype=torch.float32)
+        ids = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
+        weights = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
+        ops.moe_route(ids, weights, logits, self.router_bias, self.top)
+        return ids, weights
+
+    def apply(self, h, ctx):
+        """The chosen experts' weighted results, float32 [top, T, width]; their sum in index order is the result."""
+        ids, weights = self.route(h)
+        out = torch.empty((self.top, h.shape[0], self.width), dtype=torch.float32, device=h.device)
+        ops.moe_experts(out, h, self.w_in, self.w_out, ids, weights, self.inner, self.limit, self.alpha)
+        return out
+
+    def forward(self, h, residual, ctx):
+        ctx.then_norm = None
+        parts = self.apply(h, ctx)
+        for c in range(self.top):
+            residual.add_(parts[c])
+
+
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+register_part("feed_forward", "relu_squared", SquaredReluFeedForward)
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -61,26 +61,45 @@ class RMSNorm:
 
 
 class LayerNorm:
-    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w, no bias, statistics in 32-bit.
-    params: ``width``, ``eps``.  weights: ``weight`` [width]."""
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w (+ b with ``bias``), statistics in 32-bit.
+    params: ``width``, ``eps``, optional ``bias`` (bool).  weights: ``weight`` [width], with a bias ``bias`` [width].
+    ``add_into(residual, y)`` adds the norm of ``y`` to the 32-bit residual stream in one pass (a norm that follows a
+    sublayer); ``y`` may be [parts, T, width], whose parts are added in index order first."""
 
     graph_safe = True
 
     @classmethod
     def weight_shapes(cls, params):
-        return {"weight": ((params["width"],), "vector")}
+        shapes = {"weight": ((params["width"],), "vector")}
+        if params.get("bias"):
+            shapes["bias"] = ((params["width"],), "vector")
+        return shapes
 
     def __init__(self, params, weights, dtype, device):
         self.width = int(params["width"])
         self.eps = float(params["eps"])
         self.weight = weights["weight"]
+        self.bias = weights["bias"].to(torch.float32).contiguous() if params.get("bias") else None
+        self.weight32 = None
         self.out_dtype = torch_dtype(dtype)
+
+    def _weight32(self):
+        if self.weight32 is None:
+            self.weight32 = self.weight.to(torch.float32).contiguous()
+        return self.weight32
 
     def forward(self, x, rows=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=self.out_dtype, device=x.device)
-        ops.layernorm(out, x, self.weight, self.eps, rows)
+        if self.bias is not None:
+            ops.layernorm_affine(x, self._weight32(), self.bias, self.eps, out=out, rows=rows)
+        else:
+            ops.layernorm(out, x, self.weight, self.eps, rows)
         return out
+
+    def add_into(self, residual, y):
+        ops.layernorm_affine(y, self._weight32(), self.bias, self.eps, residual=residual,
+                             n_parts=y.shape[0] if y.dim() == 3 else 1)
 
 
 register_part("norm", "rmsnorm", RMSNorm)
