@@ -169,6 +169,12 @@ def expert(h, gate, up, down, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ down.T
 
 
+def route_margins(h, router, bias, top: int):
+    """For every token, how far the last chosen logit lies above the best one that is not chosen (inf if all are)."""
+    z = -np.sort(-(np.asarray(h, F64) @ router.T + bias), axis=-1)
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else np.full(z.shape[0], np.inf)
+
+
 def route(h, router, bias, top: int):
     """([T, top] expert numbers, [T, top] weights): the largest logits, softmax over those alone."""
     z = np.asarray(h, F64) @ router.T + bias
@@ -193,8 +199,9 @@ def _sub(tensors, prefix):
     return {k[len(prefix):]: np.asarray(v, F64) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config, tensors, tokens, layers_out=None):
-    """Logits [T, vocab] of one whole sequence.  ``layers_out``: a list that receives the stream after every layer."""
+def forward(config, tensors, tokens, layers_out=None, margins_out=None):
+    """Logits [T, vocab] of one whole sequence.  ``layers_out``: a list that receives the stream after every layer;
+    ``margins_out``: a list that receives every routed layer's ``route_margins``."""
     eps = config["norm"]["eps"]
     bg = config["embedding"]["bigram"]
     x = embed(tokens, tensors["embed"], tensors["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
@@ -222,6 +229,8 @@ def forward(config, tensors, tokens, layers_out=None):
             h = ln("norm2", x)
             w = _sub(tensors, p + "mlp.")
             y = dense_ff(h, w) if layer["mlp"]["kind"] == "dense" else moe_ff(h, w, layer["mlp"])
+            if margins_out is not None and layer["mlp"]["kind"] == "moe":
+                margins_out.append(route_margins(h, w["router"], w["router.b"], layer["mlp"]["router"]["top"]))
             x = x + ln("norm2b", y)
         if layers_out is not None:
             layers_out.append(x.copy())

@@ -27,8 +27,7 @@ __global__ void moe_route_kernel(int* __restrict__ ids, float* __restrict__ weig
     const int e = lane + 32 * i;
     z[i] = e < n_experts ? logits[(size_t)t * n_experts + e] + (bias != nullptr ? bias[e] : 0.f) : -INFINITY;
   }
-  float first = 0.f, sum = 0.f, mine = 0.f;  // lane c keeps the c-th choice's exponential
-  int mine_id = 0;
+  float first = 0.f, sum = 0.f;
   for (int c = 0; c < top; ++c) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -49,12 +48,13 @@ __global__ void moe_route_kernel(int* __restrict__ ids, float* __restrict__ weig
     if (c == 0) first = best;
     const float p = expf(best - first);  // the first choice is the largest logit
     sum += p;
-    if (lane == c) { mine = p; mine_id = best_e; }
+    if (lane == 0) {
+      ids[(size_t)t * top + c] = best_e;
+      weights[(size_t)t * top + c] = p;
+    }
   }
-  if (lane < top) {
-    ids[(size_t)t * top + lane] = mine_id;
-    weights[(size_t)t * top + lane] = mine / sum;
-  }
+  __syncwarp();
+  for (int c = lane; c < top; c += 32) weights[(size_t)t * top + c] /= sum;
 }
 
 template <typename TX, typename TW>
@@ -109,7 +109,7 @@ moe_experts_kernel(float* __restrict__ out, const TX* __restrict__ h, const TW* 
 XRT_EXPORT int xrt_moe_route(int* ids, float* weights, const float* logits, const float* bias, int n_tokens,
                              int n_experts, int top, cudaStream_t stream) {
   if (n_tokens < 0 || n_experts <= 0 || top <= 0 || top > n_experts) return XRT_ERR_ARGUMENT;
-  if (top > 32 || n_experts > 512) return XRT_ERR_UNSUPPORTED;
+  if (n_experts > 512) return XRT_ERR_UNSUPPORTED;
   if (n_tokens == 0) return XRT_OK;
   const dim3 grid((n_tokens + 3) / 4), block(128);
   if (n_experts <= 32) xrt::launch_kernel(xrt::moe_route_kernel<1>, grid, block, 0, stream, ids, weights, logits, bias, n_tokens, n_experts, top);

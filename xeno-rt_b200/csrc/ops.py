@@ -40,7 +40,7 @@ _SIGNATURES = {
     "xrt_relu_squared": [_P, _P, _I, _I, _I, _P],
     "xrt_embedding_pair": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_layernorm_affine": [_P, _P, _P, _I, ctypes.c_longlong, _P, _P, _P, _I, _I, _F, _I, _P],
-    "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I,
+    "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _I, _P, _I, _F, _I, _P, _P, _P, _I, _I, _I, _I,
                             _I, _I, _I, _I, _P],
     "xrt_decay": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
     "xrt_unit_heads": [_P, _I, _I, _I, _I, _F, _I, _F, _P],
@@ -997,11 +997,12 @@ def layernorm_affine(x, weight, bias, eps: float, out=None, residual=None, rows=
 
 def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bias, unit_norm: bool, norm_dim: int,
                     eps: float, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int, head_dim: int,
-                    v_keep=None, v_first=None, v_blend: float = 0.0, write_kv: bool = True) -> None:
+                    v_keep=None, v_first=None, v_blend: float = 0.0, v_dim: int = 0, write_kv: bool = True) -> None:
     """``qk_rope_kv_write`` without rotation for layers that add a bias a column of the q/k/v row (float32, laid out as
     the row), divide q and k heads by their root mean square without a weight (over ``norm_dim`` dims where the heads
-    are laid out wider), keep the values in 32-bit (``v_keep`` [T, kv heads * head_dim]) and / or cache
-    (1 - v_blend) v + v_blend v_first."""
+    are laid out wider), keep the values in 32-bit (``v_keep`` [T, kv heads * v_dim]) and / or cache
+    (1 - v_blend) v + v_blend v_first; ``v_dim`` (0: head_dim) is a head's true value size, at which v_keep and
+    v_first hold the heads."""
     n = qkv.shape[0]
     if q_out.shape != (n, n_heads * head_dim) or tok_slot.numel() != n or tok_pos.numel() != n:
         raise KernelError("qkv_heads_write: shapes do not fit")
@@ -1013,13 +1014,19 @@ def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bi
             raise KernelError("qkv_heads_write: the q/k/v row is too short")
     if bias is not None and bias.numel() < v_offset + n_kv_heads * head_dim:
         raise KernelError("qkv_heads_write: the bias is shorter than the q/k/v row")
-    kp, ks = _columns(v_keep, "v_keep", n_kv_heads * head_dim) if v_keep is not None else (0, 0)
-    fp, fs = _columns(v_first, "v_first", n_kv_heads * head_dim) if v_first is not None else (0, 0)
+    true_v = int(v_dim) if v_dim else head_dim
+    if not 0 < true_v <= head_dim:
+        raise KernelError("qkv_heads_write: v_dim must lie in 1 .. head_dim")
+    for t in (v_keep, v_first):
+        if t is not None and t.shape[0] != n:
+            raise KernelError("qkv_heads_write: one row of kept values a token is needed")
+    kp, ks = _columns(v_keep, "v_keep", n_kv_heads * true_v) if v_keep is not None else (0, 0)
+    fp, fs = _columns(v_first, "v_first", n_kv_heads * true_v) if v_first is not None else (0, 0)
     cache_dtype = k_pool.dtype if write_kv else q_out.dtype
     _check(_kernels().xrt_qkv_heads_write(
         _ptr(q_out, "q_out"), _ptr(k_pool if write_kv else None, "k_pool"), _ptr(v_pool if write_kv else None, "v_pool"),
         _ptr(qkv, "qkv", torch.float32), qkv.shape[1], k_offset, v_offset, _ptr(bias, "bias", torch.float32),
-        1 if unit_norm else 0, int(norm_dim), float(eps), kp, ks, fp, fs, float(v_blend),
+        1 if unit_norm else 0, int(norm_dim), float(eps), kp, ks, fp, fs, float(v_blend), true_v,
         _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
         _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim,
         1 if write_kv else 0, _code(q_out.dtype), _code(cache_dtype), _stream()), "qkv_heads_write")

@@ -49,6 +49,8 @@ __global__ void rotation_table_kernel(float2* __restrict__ cos_sin, const int* _
 //   norm_dim   the divisor of the heads' mean of squares where the heads are laid out wider than they are (0: head_dim)
 //   v_keep     the values (after the bias) are also written here in 32-bit, [tokens, v_keep_stride]
 //   v_first    the cached value is (1 - v_blend) v + v_blend v_first[token], v_first rows of v_first_stride floats
+//   v_dim      the value size of a head in v_keep and v_first, which hold the heads at their true size whatever
+//              size the layer's heads are laid out at (0: head_dim)
 struct HeadExtras {
   const float* bias = nullptr;
   int unit_norm = 0;
@@ -58,6 +60,7 @@ struct HeadExtras {
   const float* v_first = nullptr;
   int v_first_stride = 0;
   float v_blend = 0.f;
+  int v_dim = 0;
 };
 
 // One warp per (token, head) among [q heads | k heads | v heads].  MAX_PER_LANE * 32 >= head_dim.
@@ -120,13 +123,14 @@ __global__ void qk_rope_kv_write_kernel(
     for (int j = 0; j < MAX_PER_LANE; ++j) v[j] *= inv;
   }
   if (kind == 2) {
+    const int v_dim = ex.v_dim > 0 ? ex.v_dim : head_dim;
 #pragma unroll
     for (int j = 0; j < MAX_PER_LANE; ++j) {
       const int d = lane + 32 * j;
-      if (d < head_dim) {
-        if (ex.v_keep != nullptr) ex.v_keep[(size_t)t * ex.v_keep_stride + head * head_dim + d] = v[j];
+      if (d < v_dim) {
+        if (ex.v_keep != nullptr) ex.v_keep[(size_t)t * ex.v_keep_stride + head * v_dim + d] = v[j];
         if (ex.v_first != nullptr)
-          v[j] = (1.0f - ex.v_blend) * v[j] + ex.v_blend * ex.v_first[(size_t)t * ex.v_first_stride + head * head_dim + d];
+          v[j] = (1.0f - ex.v_blend) * v[j] + ex.v_blend * ex.v_first[(size_t)t * ex.v_first_stride + head * v_dim + d];
       }
     }
   }
@@ -373,7 +377,7 @@ XRT_EXPORT int xrt_qk_rope_kv_write(void* q_out, void* k_pool, void* v_pool, con
 XRT_EXPORT int xrt_qkv_heads_write(void* q_out, void* k_pool, void* v_pool, const float* qkv, int row_stride,
                                    int k_offset, int v_offset, const float* bias, int unit_norm, int norm_dim, float eps,
                                    float* v_keep, int v_keep_stride, const float* v_first, int v_first_stride,
-                                   float v_blend, const int* tok_slot, const int* tok_pos, const int* block_table,
+                                   float v_blend, int v_dim, const int* tok_slot, const int* tok_pos, const int* block_table,
                                    int max_blocks, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int write_kv,
                                    int q_dtype, int cache_dtype, cudaStream_t stream) {
   xrt::HeadExtras ex;
@@ -385,6 +389,7 @@ XRT_EXPORT int xrt_qkv_heads_write(void* q_out, void* k_pool, void* v_pool, cons
   ex.v_first = v_first;
   ex.v_first_stride = v_first_stride;
   ex.v_blend = v_blend;
+  ex.v_dim = v_dim;
   return qk_rope_kv_write(q_out, k_pool, v_pool, qkv, row_stride, k_offset, v_offset, nullptr, nullptr, eps, nullptr, 0,
                           tok_slot, tok_pos, block_table, max_blocks, n_tokens, n_heads, n_kv_heads, head_dim, write_kv,
                           0, XRT_F32, q_dtype, cache_dtype, ex, stream);

@@ -112,7 +112,7 @@ class GroupedQueryAttention:
         self.softcap = float(params.get("softcap") or 0.0)
         self.distance_rate = float(params.get("distance_rate") or 0.0)
         self.value_blend = params.get("value_blend")
-        self.true_dim = true_dim
+        self.true_dim, self.true_vdim = true_dim, true_vdim
         if self.n_heads % self.n_kv_heads:
             raise ConfigError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
         if not (16 <= self.head_dim <= 256):
@@ -217,13 +217,16 @@ class GroupedQueryAttention:
                 v_keep = v_first = None
                 if self.value_blend and owns_cache:
                     v_first = ctx.shared.get(("value_blend", self.value_blend))
+                    if v_first is not None and v_first.shape[1] != self.n_kv_heads * self.true_vdim:
+                        raise ConfigError("layers that blend their values must have the same kv heads and value size")
                     if v_first is None:  # the first layer of this name in the step: its values are the ones blended in
-                        v_keep = torch.zeros((n, self.kv_width), dtype=torch.float32, device=h.device)
+                        v_keep = torch.zeros((n, self.n_kv_heads * self.true_vdim), dtype=torch.float32, device=h.device)
                         ctx.shared[("value_blend", self.value_blend)] = v_keep
                 ops.qkv_heads_write(q, store.k, store.v, qkv, self.q_width, self.q_width + self.kv_width, self.bias,
                                     self.unit_norm, self.true_dim, self.eps, ctx.tok_slot, ctx.tok_pos, store.block_table,
                                     self.n_heads, self.n_kv_heads, self.head_dim, v_keep=v_keep, v_first=v_first,
-                                    v_blend=self.blend if v_first is not None else 0.0, write_kv=owns_cache)
+                                    v_blend=self.blend if v_first is not None else 0.0, v_dim=self.true_vdim,
+                                    write_kv=owns_cache)
             self.attend(attended, q, ctx, store)
         if self.gate == "sigmoid_head":
             ops.gate_mul(attended, projected[:, self.gate_offset:], "sigmoid", group=self.head_dim)

@@ -98,6 +98,8 @@ class LayerNorm:
         return out
 
     def add_into(self, residual, y):
+        if y.dim() == 3 and y.shape[0] == 1:
+            y = y[0]
         ops.layernorm_affine(y, self._weight32(), self.bias, self.eps, residual=residual,
                              n_parts=y.shape[0] if y.dim() == 3 else 1)
 

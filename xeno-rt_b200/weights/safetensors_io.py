@@ -136,7 +136,7 @@ def write_safetensors(path: str, tensors: dict[str, torch.Tensor], metadata: dic
         fh.write(blob)
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
-            fh.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            fh.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")  # reshape: a scalar has no dimension to view
 
 
 def write_sharded_safetensors(folder: str, tensors: dict[str, torch.Tensor], n_shards: int,
