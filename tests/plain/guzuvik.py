@@ -131,18 +131,15 @@ def attention_values(h, w, m, v_first):
     return v
 
 
-def attention(h, w, m, eps, v):
-    """``v`` from ``attention_values``."""
-    heads, kv, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+def attend(q, k, v, m):
+    """q [T, heads, dim] and k [T, kv_heads, dim] as they enter the scores, v [T, kv_heads, vdim]: every head's
+    softmax-weighted values [T, heads, vdim].  score = cap tanh(q . k scale / cap) - slope_h (i - j) over the keys
+    j that position i sees."""
+    heads, kv = q.shape[1], k.shape[1]
     size, keep = m["mask"]["size"], m["mask"]["keep_first"]
     scale, cap = m["scale"], m["softcap"]
-    h = np.asarray(h, F64)
-    n = h.shape[0]
-    q = unit_rms((h @ w["q"].T + w["q.b"]).reshape(n, heads, dim), eps)
-    k = unit_rms((h @ w["k"].T + w["k.b"]).reshape(n, kv, dim), eps)
-    v = v.reshape(n, kv, vdim)
-    gate = sigmoid(h @ w["g"].T)  # [T, heads]
-    out = np.zeros((n, heads, vdim), F64)
+    n = q.shape[0]
+    out = np.zeros((n, heads, v.shape[2]), F64)
     for head in range(heads):
         g = head // (heads // kv)
         slope = head_slope(head, heads)
@@ -153,7 +150,19 @@ def attention(h, w, m, eps, v):
             s = s - slope * (i - np.array(js, F64))
             p = np.exp(s - s.max())
             p /= p.sum()
-            out[i, head] = gate[i, head] * (p @ v[js, g])
+            out[i, head] = p @ v[js, g]
+    return out
+
+
+def attention(h, w, m, eps, v):
+    """``v`` from ``attention_values``."""
+    heads, kv, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    h = np.asarray(h, F64)
+    n = h.shape[0]
+    q = unit_rms((h @ w["q"].T + w["q.b"]).reshape(n, heads, dim), eps)
+    k = unit_rms((h @ w["k"].T + w["k.b"]).reshape(n, kv, dim), eps)
+    gate = sigmoid(h @ w["g"].T)  # [T, heads], one gate a head
+    out = attend(q, k, v.reshape(n, kv, vdim), m) * gate[:, :, None]
     return out.reshape(n, heads * vdim) @ w["o"].T
 
 
