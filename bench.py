@@ -318,6 +318,25 @@ def givopel_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: 
             "layers": [parallel if i % 2 == 0 else gla for i in range(layers)]}
 
 
+def guzuvik_config(width: int, heads: int, kv_heads: int, head_dim: int, inner: int, layers: int, vocab: int) -> dict:
+    """A Guzuvik model at the sizes of a dense decoder of that width: layers go state space + dense, attention +
+    experts, state space + experts, attention + dense, and again.  The state-space mixer has 2 * width inner channels
+    in heads of 64 with a state of 128 in 2 groups and 4 taps; attention has ``heads`` x ``head_dim`` with ``kv_heads``
+    kv heads, a window of 1,024 keys that keeps the first 4, and blended values; the dense feed-forward has ``inner``
+    units, the experts are 16 of ``inner`` / 8 units of which a token uses 2."""
+    ssm = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4, "norm_groups": 2}
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+            "softcap": 50.0, "v_mix": True, "mask": {"size": 1024, "keep_first": 4}}
+    dense = {"kind": "dense", "ff": inner}
+    moe = {"kind": "moe", "expert": {"ff": inner // 8, "limit": 7.0}, "router": {"experts": 16, "top": 2}}
+    pattern = [("mamba2", ssm, dense), ("attention", attn, moe), ("mamba2", ssm, moe), ("attention", attn, dense)]
+    return {"architecture": "Guzuvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31337, "mul_cur": 7919}},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (pattern[i % 4] for i in range(layers))]}
+
+
+DESIGN_CONFIGS = {"givopel": givopel_config, "guzuvik": guzuvik_config}
+
 DESIGN_SIZES = {
     # name: (width, heads, kv heads, head size, feed-forward width, vocabulary)
     "2k": (2048, 16, 4, 128, 8192, 32000),
@@ -326,7 +345,7 @@ DESIGN_SIZES = {
 
 
 def run_design(args) -> int:
-    """--design givopel: prompt and decode throughput of the Givopel design at sizes that resemble a real model's
+    """--design NAME: prompt and decode throughput of that design at sizes that resemble a real model's
     layers (random weights), beside the dense Llama decoder at the same width, heads, feed-forward width, layers
     and vocabulary.  One JSON line; every number device-timed as in the headline run."""
     import torch
@@ -342,19 +361,19 @@ def run_design(args) -> int:
         name = (args.design_sizes or "4k").split(",")[0]
         width, heads, kv_heads, head_dim, inner, vocab = DESIGN_SIZES[name]
         layers = args.layers or 2
-        model = Model.random(givopel_config(width, heads, kv_heads, head_dim, inner, layers, vocab), seed=0,
+        model = Model.random(DESIGN_CONFIGS[args.design](width, heads, kv_heads, head_dim, inner, layers, vocab), seed=0,
                              dtype="bfloat16", device="cuda:0")
         if args.only == "prefill":
             ms = time_prefill(model, args.prefill_tokens, iters=max(1, args.steps), warmup=args.warmup)
-            print(json.dumps({"design": "givopel", "only": "prefill", "size": name, "layers": layers,
+            print(json.dumps({"design": args.design, "only": "prefill", "size": name, "layers": layers,
                               "tokens": args.prefill_tokens, "ms": round(ms, 3)}))
         else:
             r = time_decode(model, args.batch, args.context, args.steps, args.warmup)
-            print(json.dumps({"design": "givopel", "only": "decode", "size": name, "layers": layers, "batch": args.batch,
+            print(json.dumps({"design": args.design, "only": "decode", "size": name, "layers": layers, "batch": args.batch,
                               "context": args.context, "ms_per_step": round(r["ms_per_step"], 4)}))
         return 0
     layers = args.layers or 8
-    out = {"design": "givopel", "layers": layers, "prefill_tokens": args.prefill_tokens, "decode_batch": args.batch,
+    out = {"design": args.design, "layers": layers, "prefill_tokens": args.prefill_tokens, "decode_batch": args.batch,
            "decode_context": args.context, "sizes": {}}
     for name in (args.design_sizes.split(",") if args.design_sizes else sorted(DESIGN_SIZES)):
         width, heads, kv_heads, head_dim, inner, vocab = DESIGN_SIZES[name]
@@ -362,7 +381,7 @@ def run_design(args) -> int:
                      num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
                      max_position_embeddings=max(8192, args.context, args.prefill_tokens))
         row = {}
-        for label, cfg in (("givopel", givopel_config(width, heads, kv_heads, head_dim, inner, layers, vocab)),
+        for label, cfg in ((args.design, DESIGN_CONFIGS[args.design](width, heads, kv_heads, head_dim, inner, layers, vocab)),
                            ("llama", dense)):
             model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
             prefill_ms = time_prefill(model, args.prefill_tokens, iters=5, warmup=3)
@@ -560,7 +579,7 @@ def main() -> int:
     parser.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
                         help="a short run of one part, for profiling; prints its own small JSON line "
                              "(attention: the decode attention kernel alone)")
-    parser.add_argument("--design", default="", choices=["", "givopel"],
+    parser.add_argument("--design", default="", choices=["", "givopel", "guzuvik"],
                         help="instead of the headline line: prompt and decode throughput of that design at sizes that "
                              "resemble a real model's layers, beside the dense decoder at equal sizes (--layers, default 8; "
                              "--prefill-tokens, --batch, --context, --steps as for the headline run)")

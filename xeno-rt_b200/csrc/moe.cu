@@ -8,6 +8,9 @@
 // The experts' matrices lie one after another: w_in [experts][gate rows | up rows][width], w_out [experts][width][ff].
 // xrt_moe_experts computes every (token, choice) pair in a block of its own and writes out[choice][token][width];
 // whoever follows adds a token's choices in index order, so the sum has one order whatever else is in the step.
+// For steps of many tokens the rows are sorted by expert instead (xrt_moe_group, xrt_moe_gather), every expert's rows
+// go through the library's matrix products with xrt_moe_activation between them, and xrt_moe_combine writes the same
+// out[choice][token][width].
 #include "common.cuh"
 
 namespace xrt {
@@ -41,6 +44,10 @@ __global__ void moe_route_kernel(int* __restrict__ ids, float* __restrict__ weig
       const float other = __shfl_xor_sync(0xffffffffu, best, o);
       const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
       if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    }
+    if (best_e >= n_experts) {  // a row of logits that are no numbers (a padding row's): any expert, weight as it comes
+      best_e = c;
+      best = first;
     }
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i)
@@ -103,7 +110,117 @@ moe_experts_kernel(float* __restrict__ out, const TX* __restrict__ h, const TW* 
   }
 }
 
+// ---- the same for many tokens: rows sorted by expert, one product an expert -----------------------------------
+// One block.  offsets[e] .. offsets[e + 1] are the rows of expert e in the sorted order; pos[pair] is the row of
+// (token, choice) pair `pair`, row_token[row] the token of a row.  The order of an expert's rows among themselves
+// is whatever the atomics give: no row's result depends on its neighbours.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(int* __restrict__ offsets, int* __restrict__ pos, int* __restrict__ row_token,
+                 const int* __restrict__ ids, int n_pairs, int n_experts, int top) {
+  extern __shared__ int counts[];  // [experts] counts, then [experts] cursors
+  int* cursor = counts + n_experts;
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&counts[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      offsets[e] = at;
+      cursor[e] = at;
+      at += counts[e];
+    }
+    offsets[n_experts] = at;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int row = atomicAdd(&cursor[ids[p]], 1);
+    pos[p] = row;
+    row_token[row] = p / top;
+  }
+}
+
+template <typename TX>
+__global__ void moe_gather_kernel(TX* __restrict__ out, const TX* __restrict__ h, const int* __restrict__ row_token,
+                                  int width) {
+  pdl_trigger();
+  pdl_wait();
+  const TX* src = h + (size_t)row_token[blockIdx.x] * width;
+  TX* dst = out + (size_t)blockIdx.x * width;
+  for (int k = threadIdx.x; k < width; k += blockDim.x) dst[k] = src[k];
+}
+
+// act[r, j] = g * sigmoid(alpha g) * (u + 1) with g = min(gu[r, j], limit), u = clamp(gu[r, ff + j], -limit, limit)
+template <typename TO>
+__global__ void moe_activation_kernel(TO* __restrict__ act, const float* __restrict__ gate_up, size_t total, int ff,
+                                      float limit, float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ff, j = i - r * ff;
+    const float g = fminf(gate_up[r * 2 * ff + j], limit);
+    const float u = fminf(fmaxf(gate_up[r * 2 * ff + ff + j], -limit), limit);
+    act[i] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+  }
+}
+
+// out[c][t] = weights[t][c] * y[pos[t * top + c]]
+__global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ pos,
+                                   const float* __restrict__ weights, int n_tokens, int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, c = blockIdx.y;
+  const float w = weights[(size_t)t * top + c];
+  const float* src = y + (size_t)pos[(size_t)t * top + c] * width;
+  float* dst = out + ((size_t)c * n_tokens + t) * width;
+  for (int k = threadIdx.x; k < width; k += blockDim.x) dst[k] = w * src[k];
+}
+
 }  // namespace xrt
+
+XRT_EXPORT int xrt_moe_group(int* offsets, int* pos, int* row_token, const int* ids, int n_tokens, int n_experts, int top,
+                             cudaStream_t stream) {
+  if (n_tokens < 0 || n_experts <= 0 || top <= 0) return XRT_ERR_ARGUMENT;
+  if (n_experts > 4096) return XRT_ERR_UNSUPPORTED;
+  xrt::launch_kernel(xrt::moe_group_kernel, dim3(1), dim3(1024), (size_t)2 * n_experts * sizeof(int), stream, offsets, pos,
+                     row_token, ids, n_tokens * top, n_experts, top);
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_moe_gather(void* out, const void* h, const int* row_token, int n_rows, int width, int dtype,
+                              cudaStream_t stream) {
+  if (n_rows < 0 || width <= 0) return XRT_ERR_ARGUMENT;
+  if (n_rows == 0) return XRT_OK;
+  XRT_DISPATCH_DTYPE(dtype, TX, {
+    xrt::launch_kernel(xrt::moe_gather_kernel<TX>, dim3(n_rows), dim3(128), 0, stream, (TX*)out, (const TX*)h, row_token,
+                       width);
+  });
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_moe_activation(void* act, const float* gate_up, int n_rows, int ff, float limit, float alpha,
+                                  int out_dtype, cudaStream_t stream) {
+  if (n_rows < 0 || ff <= 0) return XRT_ERR_ARGUMENT;
+  if (n_rows == 0) return XRT_OK;
+  const size_t total = (size_t)n_rows * ff;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  XRT_DISPATCH_DTYPE(out_dtype, TO, {
+    xrt::launch_kernel(xrt::moe_activation_kernel<TO>, dim3(blocks), dim3(256), 0, stream, (TO*)act, gate_up, total, ff,
+                       limit, alpha);
+  });
+  return xrt::launch_status();
+}
+
+XRT_EXPORT int xrt_moe_combine(float* out, const float* y, const int* pos, const float* weights, int n_tokens, int width,
+                               int top, cudaStream_t stream) {
+  if (n_tokens < 0 || width <= 0 || top <= 0 || top > 65535) return XRT_ERR_ARGUMENT;
+  if (n_tokens == 0) return XRT_OK;
+  xrt::launch_kernel(xrt::moe_combine_kernel, dim3(n_tokens, top), dim3(128), 0, stream, out, y, pos, weights, n_tokens,
+                     width, top);
+  return xrt::launch_status();
+}
 
 // logits [T, experts] float32 (without the bias); ids [T, top] int32 and weights [T, top] float32 are written.
 XRT_EXPORT int xrt_moe_route(int* ids, float* weights, const float* logits, const float* bias, int n_tokens,

@@ -38,6 +38,10 @@ _SIGNATURES = {
     "xrt_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_moe_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
     "xrt_relu_squared": [_P, _P, _I, _I, _I, _P],
+    "xrt_moe_group": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "xrt_moe_gather": [_P, _P, _P, _I, _I, _I, _P],
+    "xrt_moe_activation": [_P, _P, _I, _I, _F, _F, _I, _P],
+    "xrt_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_embedding_pair": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "xrt_layernorm_affine": [_P, _P, _P, _I, ctypes.c_longlong, _P, _P, _P, _I, _I, _F, _I, _P],
     "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _I, _P, _I, _F, _I, _P, _P, _P, _I, _I, _I, _I,
@@ -944,6 +948,46 @@ def moe_experts(out, h, w_in, w_out, ids, weights, ff: int, limit: float, alpha:
                                      _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32), n, width,
                                      int(ff), top, float(limit), float(alpha), _code(h.dtype), _code(w_in.dtype),
                                      _stream()), "moe_experts")
+
+
+def moe_group(offsets, pos, row_token, ids, n_experts: int) -> None:
+    """Sorts the (token, choice) pairs of ids [T, top] by expert: offsets int32 [experts + 1] (expert e's rows are
+    offsets[e] .. offsets[e + 1]), pos int32 [T * top] the row of every pair, row_token int32 [T * top] the token of
+    every row."""
+    n, top = ids.shape
+    if offsets.numel() != n_experts + 1 or pos.numel() != n * top or row_token.numel() != n * top:
+        raise KernelError("moe_group: shapes do not fit")
+    _check(_kernels().xrt_moe_group(_ptr(offsets, "offsets", torch.int32), _ptr(pos, "pos", torch.int32),
+                                   _ptr(row_token, "row_token", torch.int32), _ptr(ids, "ids", torch.int32), n,
+                                   int(n_experts), top, _stream()), "moe_group")
+
+
+def moe_gather(out, h, row_token) -> None:
+    """out[r] = h[row_token[r]]."""
+    if out.shape[1] != h.shape[1] or out.dtype != h.dtype or row_token.numel() != out.shape[0]:
+        raise KernelError("moe_gather: shapes do not fit")
+    _check(_kernels().xrt_moe_gather(_ptr(out, "out"), _ptr(h, "h"), _ptr(row_token, "row_token", torch.int32),
+                                    out.shape[0], out.shape[1], _code(h.dtype), _stream()), "moe_gather")
+
+
+def moe_activation(act, gate_up, limit: float, alpha: float) -> None:
+    """act = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up float32
+    [rows, 2 * ff] (gate columns, then up columns)."""
+    rows, ff = act.shape
+    if gate_up.shape != (rows, 2 * ff) or gate_up.dtype != torch.float32:
+        raise KernelError("moe_activation: shapes do not fit")
+    _check(_kernels().xrt_moe_activation(_ptr(act, "act"), _ptr(gate_up, "gate_up"), rows, ff, float(limit), float(alpha),
+                                        _code(act.dtype), _stream()), "moe_activation")
+
+
+def moe_combine(out, y, pos, weights) -> None:
+    """out[c, t] = weights[t, c] * y[pos[t * top + c]]; out float32 [top, T, width], y float32 [T * top, width]."""
+    top, n, width = out.shape
+    if y.shape != (n * top, width) or pos.numel() != n * top or weights.shape != (n, top):
+        raise KernelError("moe_combine: shapes do not fit")
+    _check(_kernels().xrt_moe_combine(_ptr(out, "out", torch.float32), _ptr(y, "y", torch.float32),
+                                     _ptr(pos, "pos", torch.int32), _ptr(weights, "weights", torch.float32), n, width, top,
+                                     _stream()), "moe_combine")
 
 
 def relu_squared(out, x) -> None:

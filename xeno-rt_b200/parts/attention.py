@@ -199,7 +199,8 @@ class GroupedQueryAttention:
         pairing = getattr(self.position, "pairing", "split_half")
         cos_sin = self.position.tables(ctx)
         # padding rows belong to no sequence: kernels that walk sequences leave them unwritten
-        padded = sum(ctx.new_lens) < ctx.n_tokens
+        # a captured step is replayed with padding rows, which the kernel of the scored layers leaves unwritten
+        padded = (getattr(ctx, "captured", False) and not self.plain_scores) or sum(ctx.new_lens) < ctx.n_tokens
         attended = (torch.zeros if padded else torch.empty)((n, self.q_width), dtype=self.act_dtype, device=h.device)
         if self.dtype is DType.BF16 and self.plain_heads and self.plain_scores:
             from . import attention_bf16

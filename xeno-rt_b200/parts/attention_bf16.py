@@ -94,8 +94,8 @@ def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window, keep_f
     if n_heads // n_kv_heads > 16:
         return False
     scored = bool(keep_first or softcap or distance_rate)  # the layer's score options: kernels that take them only
-    if scored:
-        if ctx.all_single or head_dim % 16 or ctx.n_seqs > 65535 or n_heads > 65535:
+    if scored:  # single tokens too: a tile of 64 query rows of which one is live, over the window's tiles
+        if head_dim % 16 or ctx.n_seqs > 65535 or n_heads > 65535:
             return False
         ops.attention_prefill(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
                               store.block_table, ctx.max_new, n_heads, n_kv_heads, head_dim, scale, window,

@@ -137,11 +137,36 @@ class RoutedExperts:
         ops.moe_route(ids, weights, logits, self.router_bias, self.top)
         return ids, weights
 
+    GROUPED_FROM = 4  # (token, choice) pairs an expert from which a step's rows are sorted by expert
+
     def apply(self, h, ctx):
-        """The chosen experts' weighted results, float32 [top, T, width]; their sum in index order is the result."""
+        """The chosen experts' weighted results, float32 [top, T, width]; their sum in index order is the result.
+        A step of few tokens runs every (token, choice) pair in a block of its own, which streams that expert's
+        matrices (a captured decode step: no size depends on the choices).  A step of many tokens sorts its rows by
+        expert and runs one pair of matrix products an expert; how many rows each expert has is read back once."""
+        n = h.shape[0]
         ids, weights = self.route(h)
-        out = torch.empty((self.top, h.shape[0], self.width), dtype=torch.float32, device=h.device)
-        ops.moe_experts(out, h, self.w_in, self.w_out, ids, weights, self.inner, self.limit, self.alpha)
+        out = torch.empty((self.top, n, self.width), dtype=torch.float32, device=h.device)
+        if getattr(ctx, "captured", False) or ctx.all_single or n * self.top < self.GROUPED_FROM * self.experts:
+            ops.moe_experts(out, h, self.w_in, self.w_out, ids, weights, self.inner, self.limit, self.alpha)
+            return out
+        pairs = n * self.top
+        offsets = torch.empty((self.experts + 1,), dtype=torch.int32, device=h.device)
+        pos = torch.empty((pairs,), dtype=torch.int32, device=h.device)
+        row_token = torch.empty((pairs,), dtype=torch.int32, device=h.device)
+        ops.moe_group(offsets, pos, row_token, ids, self.experts)
+        rows = torch.empty((pairs, self.width), dtype=h.dtype, device=h.device)
+        ops.moe_gather(rows, h, row_token)
+        bounds = offsets.tolist()  # the one wait of the host for the device in this part
+        act = torch.empty((pairs, self.inner), dtype=h.dtype, device=h.device)
+        y = torch.zeros((pairs, self.width), dtype=torch.float32, device=h.device)
+        for e in range(self.experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                gate_up = linear(rows[lo:hi], self.w_in[e * 2 * self.inner:(e + 1) * 2 * self.inner], out_dtype=torch.float32)
+                ops.moe_activation(act[lo:hi], gate_up, self.limit, self.alpha)
+                linear(act[lo:hi], self.w_out[e * self.width:(e + 1) * self.width], accumulate_into=y[lo:hi])
+        ops.moe_combine(out, y, pos, weights)
         return out
 
     def forward(self, h, residual, ctx):
