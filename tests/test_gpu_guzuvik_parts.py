@@ -224,6 +224,16 @@ def test_scores_with_a_window_kept_first_tokens_a_cap_and_a_distance_slope(dtype
             ops.attention_prefill(out, qd[start:].contiguous(), kp, vp, _ints([0, n - start]), _ints([2]), _ints([start]),
                                   table, n - start, heads, kv, size, m["scale"], window, **options)
             _close(out.float().cpu().numpy(), want[start:], tol)
+        # single tokens: every position as a step's one new token, the visible keys cut into stretches or not
+        for chunk, splits in ((32, 11), (128, 3), (352, 1)):
+            if chunk * splits >= (window + keep if window < n else n):
+                out = torch.empty_like(qd)
+                slots = _ints([2] * (n - 1) + [-1])  # the last row belongs to no sequence: zeros
+                ops.attention_decode_scored(out, qd, kp, vp, slots, _ints(range(n)), table, heads, kv, size, m["scale"],
+                                            window, keep, cap, 8.0, chunk, splits)
+                got = out.float().cpu().numpy()
+                _close(got[:-1], want[:-1], tol)
+                assert not got[-1].any()
     # without the options the window alone decides: the kept first tokens must then be gone
     if keep and window + keep < n:
         plain_m = {"mask": {"size": window, "keep_first": 0}, "scale": m["scale"], "softcap": cap}

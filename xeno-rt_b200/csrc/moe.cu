@@ -6,7 +6,9 @@
 //             result W_down y, times the token's weight for that expert
 //
 // The experts' matrices lie one after another: w_in [experts][gate rows | up rows][width], w_out [experts][width][ff].
-// xrt_moe_experts computes every (token, choice) pair in a block of its own and writes out[choice][token][width];
+// xrt_moe_experts computes every (token, choice) pair by itself (two kernels: the gated hidden units, then the
+// output rows; blocks of 32 units or rows each stream their part of the expert's matrices) and writes
+// out[choice][token][width];
 // whoever follows adds a token's choices in index order, so the sum has one order whatever else is in the step.
 // For steps of many tokens the rows are sorted by expert instead (xrt_moe_group, xrt_moe_gather), every expert's rows
 // go through the library's matrix products with xrt_moe_activation between them, and xrt_moe_combine writes the same
@@ -64,48 +66,74 @@ __global__ void moe_route_kernel(int* __restrict__ ids, float* __restrict__ weig
   for (int c = lane; c < top; c += 32) weights[(size_t)t * top + c] /= sum;
 }
 
-template <typename TX, typename TW>
+// Dot product of a weight row with a vector in shared memory, 16 bytes of the row a lane and step where VEC
+// (the row's length a multiple of 16 bytes' worth and the row 16-byte aligned), else one element a lane and step.
+template <typename TW, bool VEC>
+__device__ __forceinline__ float row_dot(const TW* __restrict__ row, const float* __restrict__ x, int n, int lane) {
+  constexpr int PER = 16 / (int)sizeof(TW);
+  float acc = 0.f;
+  if (VEC) {
+    for (int k = lane * PER; k < n; k += 32 * PER) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(row + k);
+      const TW* v = reinterpret_cast<const TW*>(&raw);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) acc = fmaf(to_float(v[j]), x[k + j], acc);
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) acc = fmaf(to_float(row[k]), x[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+// First half of a (token, choice) pair: act[pair][j] for the hidden units j of this block (UNITS a block, one warp a
+// unit at a time).  grid (tokens, top, ceil(ff / UNITS)).
+constexpr int MOE_UNITS = 32;
+template <typename TX, typename TW, bool VEC>
 __global__ void __launch_bounds__(256)
-moe_experts_kernel(float* __restrict__ out, const TX* __restrict__ h, const TW* __restrict__ w_in,
-                   const TW* __restrict__ w_out, const int* __restrict__ ids, const float* __restrict__ weights,
-                   int n_tokens, int width, int ff, int top, float limit, float alpha) {
-  extern __shared__ float staged[];  // h [width] | y [ff]
-  float* hs = staged;
-  float* ys = staged + width;
+moe_experts_in_kernel(float* __restrict__ act, const TX* __restrict__ h, const TW* __restrict__ w_in,
+                      const int* __restrict__ ids, int width, int ff, int top, float limit, float alpha) {
+  extern __shared__ float hs[];  // [width]
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, c = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int e = ids[(size_t)t * top + c];
+  for (int k = threadIdx.x; k < width; k += blockDim.x) hs[k] = to_float(h[(size_t)t * width + k]);
+  __syncthreads();
+  const TW* gate = w_in + (size_t)e * 2 * ff * width;
+  const TW* up = gate + (size_t)ff * width;
+  const int j1 = min(ff, (int)(blockIdx.z + 1) * MOE_UNITS);
+  for (int j = blockIdx.z * MOE_UNITS + warp; j < j1; j += n_warps) {
+    float g = row_dot<TW, VEC>(gate + (size_t)j * width, hs, width, lane);
+    float u = row_dot<TW, VEC>(up + (size_t)j * width, hs, width, lane);
+    if (lane == 0) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      act[((size_t)t * top + c) * ff + j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+  }
+}
+
+// Second half: out[c][t][r] = weight * (W_down[e] act)[r] for the rows r of this block.  grid (tokens, top, ceil(width / UNITS)).
+template <typename TW, bool VEC>
+__global__ void __launch_bounds__(256)
+moe_experts_out_kernel(float* __restrict__ out, const float* __restrict__ act, const TW* __restrict__ w_out,
+                       const int* __restrict__ ids, const float* __restrict__ weights, int n_tokens, int width, int ff,
+                       int top) {
+  extern __shared__ float ys[];  // [ff]
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const int e = ids[(size_t)t * top + c];
   const float weight = weights[(size_t)t * top + c];
-  for (int k = threadIdx.x; k < width; k += blockDim.x) hs[k] = to_float(h[(size_t)t * width + k]);
-  __syncthreads();
-  const TW* gate = w_in + (size_t)e * 2 * ff * width;
-  const TW* up = gate + (size_t)ff * width;
-  for (int j = warp; j < ff; j += n_warps) {
-    const TW* gr = gate + (size_t)j * width;
-    const TW* ur = up + (size_t)j * width;
-    float g = 0.f, u = 0.f;
-    for (int k = lane; k < width; k += 32) {
-      g = fmaf(to_float(gr[k]), hs[k], g);
-      u = fmaf(to_float(ur[k]), hs[k], u);
-    }
-    g = warp_sum(g);
-    u = warp_sum(u);
-    if (lane == 0) {
-      g = fminf(g, limit);
-      u = fminf(fmaxf(u, -limit), limit);
-      ys[j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
-    }
-  }
+  for (int k = threadIdx.x; k < ff; k += blockDim.x) ys[k] = act[((size_t)t * top + c) * ff + k];
   __syncthreads();
   const TW* down = w_out + (size_t)e * width * ff;
   float* dst = out + ((size_t)c * n_tokens + t) * width;
-  for (int r = warp; r < width; r += n_warps) {
-    const TW* dr = down + (size_t)r * ff;
-    float acc = 0.f;
-    for (int k = lane; k < ff; k += 32) acc = fmaf(to_float(dr[k]), ys[k], acc);
-    acc = warp_sum(acc);
+  const int r1 = min(width, (int)(blockIdx.z + 1) * MOE_UNITS);
+  for (int r = blockIdx.z * MOE_UNITS + warp; r < r1; r += n_warps) {
+    const float acc = row_dot<TW, VEC>(down + (size_t)r * ff, ys, ff, lane);
     if (lane == 0) dst[r] = weight * acc;
   }
 }
@@ -237,24 +265,33 @@ XRT_EXPORT int xrt_moe_route(int* ids, float* weights, const float* logits, cons
   return xrt::launch_status();
 }
 
-// out [top, T, width] float32; h [T, width]; w_in [experts * 2 * ff, width]; w_out [experts * width, ff].
-XRT_EXPORT int xrt_moe_experts(float* out, const void* h, const void* w_in, const void* w_out, const int* ids,
+// out [top, T, width] float32; h [T, width]; w_in [experts * 2 * ff, width]; w_out [experts * width, ff];
+// act [T * top, ff] float32 scratch between the two halves.
+XRT_EXPORT int xrt_moe_experts(float* out, float* act, const void* h, const void* w_in, const void* w_out, const int* ids,
                                const float* weights, int n_tokens, int width, int ff, int top, float limit, float alpha,
                                int h_dtype, int w_dtype, cudaStream_t stream) {
   if (n_tokens < 0 || width <= 0 || ff <= 0 || top <= 0) return XRT_ERR_ARGUMENT;
-  if (top > 65535) return XRT_ERR_UNSUPPORTED;
+  if (top > 65535 || (ff + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS > 65535 || (width + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS > 65535)
+    return XRT_ERR_UNSUPPORTED;
   if (n_tokens == 0) return XRT_OK;
-  const size_t smem = (size_t)(width + ff) * sizeof(float);
-  if (smem > 200 * 1024) return XRT_ERR_UNSUPPORTED;
+  if ((size_t)(width > ff ? width : ff) * sizeof(float) > 48 * 1024) return XRT_ERR_UNSUPPORTED;
+  const int per = w_dtype == XRT_BF16 ? 8 : 4;
+  const bool vec = width % per == 0 && ff % per == 0 && (((uintptr_t)w_in | (uintptr_t)w_out) & 15) == 0;
+  const dim3 grid_in(n_tokens, top, (ff + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS);
+  const dim3 grid_out(n_tokens, top, (width + xrt::MOE_UNITS - 1) / xrt::MOE_UNITS);
   XRT_DISPATCH_DTYPE(h_dtype, TX, {
     XRT_DISPATCH_DTYPE(w_dtype, TW, {
-      auto kernel = xrt::moe_experts_kernel<TX, TW>;
-      if (smem > 48 * 1024) {
-        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) return (int)err;
+      if (vec) {
+        xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, true>, grid_in, dim3(256), (size_t)width * sizeof(float), stream,
+                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha);
+        xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, true>, grid_out, dim3(256), (size_t)ff * sizeof(float), stream, out,
+                           (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);
+      } else {
+        xrt::launch_kernel(xrt::moe_experts_in_kernel<TX, TW, false>, grid_in, dim3(256), (size_t)width * sizeof(float), stream,
+                           act, (const TX*)h, (const TW*)w_in, ids, width, ff, top, limit, alpha);
+        xrt::launch_kernel(xrt::moe_experts_out_kernel<TW, false>, grid_out, dim3(256), (size_t)ff * sizeof(float), stream, out,
+                           (const float*)act, (const TW*)w_out, ids, weights, n_tokens, width, ff, top);
       }
-      xrt::launch_kernel(kernel, dim3(n_tokens, top), dim3(256), smem, stream, out, (const TX*)h, (const TW*)w_in,
-                         (const TW*)w_out, ids, weights, n_tokens, width, ff, top, limit, alpha);
     });
   });
   return xrt::launch_status();

@@ -36,7 +36,7 @@ _SIGNATURES = {
     "xrt_ssd_scan": [_P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "xrt_gated_group_norm": [_P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _P],
     "xrt_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
-    "xrt_moe_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+    "xrt_moe_experts": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
     "xrt_relu_squared": [_P, _P, _I, _I, _I, _P],
     "xrt_moe_group": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_moe_gather": [_P, _P, _P, _I, _I, _I, _P],
@@ -71,6 +71,7 @@ _SIGNATURES = {
     "xrt_attention_decode": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
     "xrt_attention_decode_qkv": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I,
                                  _I, _I, _F, _I, _I, _I, _P, _P, _P, _I],
+    "xrt_attention_decode_scored": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _I, _I, _P],
     "xrt_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F, _F, _P],
     "xrt_attention_prefill_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "xrt_fill_normal": [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, _I, _P],
@@ -695,6 +696,29 @@ def attention_prefill(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, b
         _stream()), "attention_prefill")
 
 
+def attention_decode_scored(out, q, k_pool, v_pool, tok_slot, tok_pos, block_table, n_heads: int, n_kv_heads: int,
+                            head_dim: int, scale: float, window: int, keep_first: int, softcap: float, distance_rate: float,
+                            chunk: int, n_splits: int) -> None:
+    """bfloat16 attention of single new tokens with the score options of ``attention_reference``; a token's visible
+    keys (kept first keys, then the window) are cut into ``n_splits`` stretches of ``chunk`` keys (a multiple of 32)."""
+    n = q.shape[0]
+    if q.shape != (n, n_heads * head_dim) or out.shape != q.shape or tok_slot.numel() != n or tok_pos.numel() != n:
+        raise KernelError("attention_decode_scored: shapes do not fit")
+    if k_pool.shape != v_pool.shape or k_pool.shape[1:] != (n_kv_heads, 64, head_dim):
+        raise KernelError("attention_decode_scored: the cache pool must be [blocks, kv heads, 64, head_dim]")
+    partial = None
+    if n_splits > 1:
+        partial = torch.empty((n, n_heads, n_splits, head_dim + 2), dtype=torch.float32, device=q.device)
+        add_launches(1)
+    _check(_kernels().xrt_attention_decode_scored(
+        _ptr(out, "out", torch.bfloat16), _ptr(partial, "partial"), _ptr(q, "q", torch.bfloat16),
+        _ptr(k_pool, "k_pool", torch.bfloat16), _ptr(v_pool, "v_pool", torch.bfloat16),
+        _ptr(tok_slot, "tok_slot", torch.int32), _ptr(tok_pos, "tok_pos", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1], n, n_heads, n_kv_heads, head_dim, float(scale),
+        int(window), int(keep_first), float(softcap), float(distance_rate), int(chunk), int(n_splits), _stream()),
+        "attention_decode_scored")
+
+
 def attention_prefill_tcgen05(out, q, k_pool, v_pool, cu_seqlens, seq_slot, seq_start, block_table, max_new: int,
                               n_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> None:
     """bfloat16 causal attention of sequences laid end to end on the tcgen05 tensor cores (head size 128)."""
@@ -944,7 +968,9 @@ def moe_experts(out, h, w_in, w_out, ids, weights, ff: int, limit: float, alpha:
         raise KernelError("moe_experts: shapes do not fit")
     if w_in.shape[0] % (2 * ff) or w_out.shape[0] != w_in.shape[0] // (2 * ff) * width or out.dtype != torch.float32:
         raise KernelError("moe_experts: the experts' matrices do not fit")
-    _check(_kernels().xrt_moe_experts(_ptr(out, "out"), _ptr(h, "h"), _ptr(w_in, "w_in"), _ptr(w_out, "w_out", w_in.dtype),
+    act = torch.empty((n * top, ff), dtype=torch.float32, device=out.device)  # the hidden units, between the two kernels
+    add_launches(1)
+    _check(_kernels().xrt_moe_experts(_ptr(out, "out"), _ptr(act, "act"), _ptr(h, "h"), _ptr(w_in, "w_in"), _ptr(w_out, "w_out", w_in.dtype),
                                      _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32), n, width,
                                      int(ff), top, float(limit), float(alpha), _code(h.dtype), _code(w_in.dtype),
                                      _stream()), "moe_experts")

@@ -89,12 +89,29 @@ def decode_from_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, 
     return True
 
 
+def scored_decode_split(n_tokens: int, n_kv_heads: int, context: int, window: int, keep_first: int, sms: int):
+    """(keys a split, splits) for the single-token kernel of the scored layers: the most keys a token can see (the
+    window or the context, and the kept first keys) in stretches of a multiple of 128 keys (32 a warp), as many as
+    give every multiprocessor about two blocks."""
+    most = (min(window, context) if window > 0 else context) + (keep_first if window > 0 else 0)
+    pairs = max(1, n_tokens * n_kv_heads)
+    splits = max(1, min(-(-2 * sms // pairs), -(-most // 128), 64))
+    chunk = -(-(-(-most // splits)) // 128) * 128
+    return chunk, -(-most // chunk)
+
+
 def run(out, q, ctx, store, n_heads, n_kv_heads, head_dim, scale, window, keep_first=0, softcap=0.0,
         distance_rate=0.0) -> bool:
     if n_heads // n_kv_heads > 16:
         return False
     scored = bool(keep_first or softcap or distance_rate)  # the layer's score options: kernels that take them only
-    if scored:  # single tokens too: a tile of 64 query rows of which one is live, over the window's tiles
+    if scored and ctx.all_single and head_dim % 8 == 0 and n_kv_heads <= 65535:
+        chunk, n_splits = scored_decode_split(ctx.n_tokens, n_kv_heads, context_bucket(ctx.max_context), window,
+                                              keep_first, ops.device_state(q.device)[2])
+        ops.attention_decode_scored(out, q, store.k, store.v, ctx.tok_slot, ctx.tok_pos, store.block_table, n_heads,
+                                    n_kv_heads, head_dim, scale, window, keep_first, softcap, distance_rate, chunk, n_splits)
+        return True
+    if scored:
         if head_dim % 16 or ctx.n_seqs > 65535 or n_heads > 65535:
             return False
         ops.attention_prefill(out, q, store.k, store.v, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
