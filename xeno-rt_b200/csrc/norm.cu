@@ -190,11 +190,14 @@ __global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__
 
 // Layer norm with a weight and an optional bias over the sum of `n_parts` inputs (x + p * part_stride, added in index
 // order), y = (x - mean) / sqrt(var + eps) * w + b.  With `residual` the result is added to that 32-bit row instead of
-// written to `out`: a norm that follows a sublayer, and the residual sum, in one pass.  The row is kept in shared memory.
+// written to `out`: a norm that follows a sublayer, and the residual sum, in one pass; with `residual` AND `out` the
+// new residual row is then normed again with (w2, b2) into `out`: the norm that the next sublayer begins with.
+// The row is kept in shared memory.
 template <typename TO>
 __global__ void layernorm_affine_kernel(TO* __restrict__ out, float* __restrict__ residual, const float* __restrict__ x,
                                         int n_parts, size_t part_stride, const float* __restrict__ w,
-                                        const float* __restrict__ b, const int* __restrict__ rows, int width, float eps) {
+                                        const float* __restrict__ b, const int* __restrict__ rows, int width, float eps,
+                                        const float* __restrict__ w2, const float* __restrict__ b2) {
   extern __shared__ float row[];
   __shared__ float scratch[33];
   pdl_trigger();
@@ -209,26 +212,45 @@ __global__ void layernorm_affine_kernel(TO* __restrict__ out, float* __restrict_
     row[c] = v;
     acc += v;
   }
-  const float mean = block_sum(acc, scratch) / (float)width;
+  float mean = block_sum(acc, scratch) / (float)width;
   acc = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float d = row[c] - mean;
     acc = fmaf(d, d, acc);
   }
-  const float inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  float inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  acc = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float y = ((row[c] - mean) * inv) * w[c] + (b != nullptr ? b[c] : 0.f);
-    if (residual != nullptr) residual[(size_t)r * width + c] += y;
-    else out[(size_t)r * width + c] = from_float<TO>(y);
+    if (residual != nullptr) {
+      const float sum = residual[(size_t)r * width + c] + y;
+      residual[(size_t)r * width + c] = sum;
+      row[c] = sum;  // a thread reads back only what it wrote
+      acc += sum;
+    } else {
+      out[(size_t)r * width + c] = from_float<TO>(y);
+    }
   }
+  if (residual == nullptr || out == nullptr) return;
+  mean = block_sum(acc, scratch) / (float)width;
+  acc = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float d = row[c] - mean;
+    acc = fmaf(d, d, acc);
+  }
+  inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(size_t)r * width + c] = from_float<TO>(((row[c] - mean) * inv) * w2[c] + (b2 != nullptr ? b2[c] : 0.f));
 }
 
 }  // namespace xrt
 
 XRT_EXPORT int xrt_layernorm_affine(void* out, float* residual, const float* x, int n_parts, long long part_stride,
                                     const float* weight, const float* bias, const int* rows, int n_rows, int width,
-                                    float eps, int out_dtype, cudaStream_t stream) {
-  if (n_rows < 0 || width <= 0 || n_parts < 1 || (out == nullptr) == (residual == nullptr)) return XRT_ERR_ARGUMENT;
+                                    float eps, int out_dtype, const float* weight2, const float* bias2,
+                                    cudaStream_t stream) {
+  if (n_rows < 0 || width <= 0 || n_parts < 1 || (out == nullptr && residual == nullptr)) return XRT_ERR_ARGUMENT;
+  if (out != nullptr && residual != nullptr && (weight2 == nullptr || rows != nullptr)) return XRT_ERR_ARGUMENT;
   if ((size_t)width * sizeof(float) > 160 * 1024) return XRT_ERR_UNSUPPORTED;
   if (n_rows == 0) return XRT_OK;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
@@ -240,7 +262,7 @@ XRT_EXPORT int xrt_layernorm_affine(void* out, float* residual, const float* x, 
       if (err != cudaSuccess) return (int)err;
     }
     xrt::launch_kernel(kernel, dim3(n_rows), dim3(threads), smem, stream, (TO*)out, residual, x, n_parts,
-                       (size_t)part_stride, weight, bias, rows, width, eps);
+                       (size_t)part_stride, weight, bias, rows, width, eps, weight2, bias2);
   });
   return xrt::launch_status();
 }

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "xrt_moe_activation": [_P, _P, _I, _I, _F, _F, _I, _P],
     "xrt_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_embedding_pair": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "xrt_layernorm_affine": [_P, _P, _P, _I, ctypes.c_longlong, _P, _P, _P, _I, _I, _F, _I, _P],
+    "xrt_layernorm_affine": [_P, _P, _P, _I, ctypes.c_longlong, _P, _P, _P, _I, _I, _F, _I, _P, _P, _P],
     "xrt_qkv_heads_write": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _I, _P, _I, _F, _I, _P, _P, _P, _I, _I, _I, _I,
                             _I, _I, _I, _I, _P],
     "xrt_decay": [_P, _P, _P, _I, _I, _I, _I, _F, _P],
@@ -1043,14 +1043,18 @@ def embedding_pair(out, table, pairs, ids, tok_slot, tok_pos, last_token, cu_seq
     add_launches(1)
 
 
-def layernorm_affine(x, weight, bias, eps: float, out=None, residual=None, rows=None, n_parts: int = 1) -> None:
+def layernorm_affine(x, weight, bias, eps: float, out=None, residual=None, rows=None, n_parts: int = 1, then=None) -> None:
     """y = (x - mean) / sqrt(variance + eps) * weight + bias over float32 rows; written to ``out`` (any dtype), or
-    added into ``residual`` (float32) when that is given.  ``x`` may be [n_parts, T, width]: the parts are added in
-    index order first.  ``rows`` gathers rows of x."""
+    added into ``residual`` (float32) when that is given.  With ``residual``, ``out`` and ``then`` = (weight2, bias2)
+    the new residual rows are normed once more, with those, into ``out`` (the norm the next sublayer begins with).
+    ``x`` may be [n_parts, T, width]: the parts are added in index order first.  ``rows`` gathers rows of x."""
     width = x.shape[-1]
-    target = out if out is not None else residual
-    if (out is None) == (residual is None) or target.shape[-1] != width or x.dtype != torch.float32:
-        raise KernelError("layernorm_affine: give out or residual, of x's width")
+    target = residual if residual is not None else out
+    both = out is not None and residual is not None
+    if target is None or target.shape[-1] != width or x.dtype != torch.float32 or both != (then is not None):
+        raise KernelError("layernorm_affine: give out or residual of x's width, or both with the second norm")
+    if both and (out.shape != residual.shape or rows is not None or then[0].numel() != width):
+        raise KernelError("layernorm_affine: the second norm needs rows of the residual's shape")
     if x.dim() != (3 if n_parts > 1 else 2) or (n_parts > 1 and x.shape[0] != n_parts) or not x.is_contiguous():
         raise KernelError("layernorm_affine: x must be [T, width] or [parts, T, width]")
     n_rows = target.shape[0]
@@ -1062,7 +1066,10 @@ def layernorm_affine(x, weight, bias, eps: float, out=None, residual=None, rows=
                                           int(n_parts), x.shape[-2] * width if n_parts > 1 else 0,
                                           _ptr(weight, "weight", torch.float32), _ptr(bias, "bias", torch.float32),
                                           _ptr(rows, "rows", torch.int32), n_rows, width, float(eps),
-                                          _code(out.dtype) if out is not None else 0, _stream()), "layernorm_affine")
+                                          _code(out.dtype) if out is not None else 0,
+                                          _ptr(then[0] if then else None, "weight2", torch.float32),
+                                          _ptr(then[1] if then else None, "bias2", torch.float32), _stream()),
+           "layernorm_affine")
 
 
 def qkv_heads_write(q_out, k_pool, v_pool, qkv, k_offset: int, v_offset: int, bias, unit_norm: bool, norm_dim: int,

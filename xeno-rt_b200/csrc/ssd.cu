@@ -32,7 +32,7 @@ struct SsdArgs {
 // `tile_tokens` tokens' b, c, x, step size and decay are staged in shared memory.
 template <int R>
 __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
-  extern __shared__ float tile[];
+  extern __shared__ __align__(16) float tile[];
   pdl_trigger();
   pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y;
@@ -79,11 +79,26 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
       sdecay[tt] = expf(-rate * dt);
     }
     __syncthreads();
+#pragma unroll 4
     for (int tt = 0; tt < nt; ++tt) {
       const float xv = sx[tt * cols + jl];
       const float decay = sdecay[tt], u = sdt[tt] * xv;
-      const float* bt = sb + tt * padded + part * R;
-      const float* ct = sc + tt * padded + part * R;
+      float bt[R], ct[R];
+      if (R % 4 == 0) {  // a lane's rows of b and c as whole 16 bytes
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(sb + tt * padded + part * R + i);
+          const float4 c4 = *reinterpret_cast<const float4*>(sc + tt * padded + part * R + i);
+          bt[i] = b4.x; bt[i + 1] = b4.y; bt[i + 2] = b4.z; bt[i + 3] = b4.w;
+          ct[i] = c4.x; ct[i + 1] = c4.y; ct[i + 2] = c4.z; ct[i + 3] = c4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          bt[i] = sb[tt * padded + part * R + i];
+          ct[i] = sc[tt * padded + part * R + i];
+        }
+      }
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
       for (int i = 0; i < R; ++i) {
@@ -156,7 +171,7 @@ XRT_EXPORT int xrt_ssd_scan(float* out, const float* x, int x_stride, const floa
   int threads = 128;
   while (threads > 32 && threads / parts >= 2 * vdim) threads /= 2;  // no more lanes than the columns need
   a.cols = threads / parts;
-  a.tile_tokens = max_new < 16 ? max_new : 16;
+  a.tile_tokens = max_new < 32 ? max_new : 32;
   while (a.tile_tokens > 1 && (size_t)a.tile_tokens * (2 * parts * r + a.cols + 2) * sizeof(float) > 40 * 1024)
     a.tile_tokens /= 2;
   const size_t smem = ((size_t)a.tile_tokens * (2 * parts * r + a.cols + 2)) * sizeof(float);

@@ -74,17 +74,33 @@ def sandwich_residual(parts: LayerParts, x, ctx, stores, owns_cache: bool) -> No
     """x += post_norm(mixer(norm(x))); x += post_norm(feed_forward(norm(x))): a norm before and after each sublayer.
     The layer's parts are ``mixer_norm``, ``mixer``, ``mixer_post`` and, if it has a feed-forward, ``ffn_norm``,
     ``ffn``, ``ffn_post``.  The mixer hands its result back (``mix``), the feed-forward too (``apply``: [T, width] or
-    [parts, T, width] float32), and the norm after it adds into the 32-bit stream (``add_into``)."""
+    [parts, T, width] float32), and the norm after it adds into the 32-bit stream (``add_into``).
+    The norm after a sublayer also computes the norm that the next sublayer begins with, in the same pass over the
+    row (its own feed-forward's, or the first norm of the layer that runs next, left in ``ctx.pending``)."""
+    ready = ctx.take_pending(parts.mixer_norm)
+    h = ready.value if ready is not None else parts.mixer_norm.forward(x)
+    after = ctx.shared.get("next_layer")  # (first norm, the part that takes it) of the layer that runs next, or None
+    has_ffn = "ffn" in parts
+    following = parts.ffn_norm if has_ffn else (after[0] if after else None)
+    h = parts.mixer_post.add_into(x, parts.mixer.mix(h, ctx, stores.get("mixer"), owns_cache), then=following)
     ctx.then_norm = ctx.pending = None
-    h = parts.mixer_norm.forward(x)
-    parts.mixer_post.add_into(x, parts.mixer.mix(h, ctx, stores.get("mixer"), owns_cache))
-    ctx.then_norm = ctx.pending = None
-    if "ffn" in parts:
-        h = parts.ffn_norm.forward(x)
-        parts.ffn_post.add_into(x, parts.ffn.apply(h, ctx))
-        ctx.then_norm = ctx.pending = None
+    if has_ffn:
+        if h is None:
+            h = parts.ffn_norm.forward(x)
+        following = after[0] if after else None
+        h = parts.ffn_post.add_into(x, parts.ffn.apply(h, ctx), then=following)
+    if h is not None:
+        ctx.pending = ReadyNorm(following, h)
 
 
+class ReadyNorm:
+    """A norm's finished result that the part before it computed on its way: ``norm`` is the part it stands for."""
+
+    def __init__(self, norm, value):
+        self.norm, self.value = norm, value
+
+
+sandwich_residual.first_norm = lambda parts: (parts.mixer_norm, parts.mixer)
 register_part("arrangement", "parallel_residual", parallel_residual)
 register_part("arrangement", "sandwich_residual", sandwich_residual)
 

@@ -97,11 +97,19 @@ class LayerNorm:
             ops.layernorm(out, x, self.weight, self.eps, rows)
         return out
 
-    def add_into(self, residual, y):
+    def add_into(self, residual, y, then=None):
+        """residual += norm(y).  ``then``: another LayerNorm of the same width and eps; its result over the new
+        residual is returned (computed in the same pass), else None."""
         if y.dim() == 3 and y.shape[0] == 1:
             y = y[0]
-        ops.layernorm_affine(y, self._weight32(), self.bias, self.eps, residual=residual,
-                             n_parts=y.shape[0] if y.dim() == 3 else 1)
+        parts = y.shape[0] if y.dim() == 3 else 1
+        if isinstance(then, LayerNorm) and then.width == self.width and then.eps == self.eps:
+            out = torch.empty(residual.shape, dtype=then.out_dtype, device=residual.device)
+            ops.layernorm_affine(y, self._weight32(), self.bias, self.eps, out=out, residual=residual, n_parts=parts,
+                                 then=(then._weight32(), then.bias))
+            return out
+        ops.layernorm_affine(y, self._weight32(), self.bias, self.eps, residual=residual, n_parts=parts)
+        return None
 
 
 register_part("norm", "rmsnorm", RMSNorm)
