@@ -193,13 +193,27 @@ __global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__
 // written to `out`: a norm that follows a sublayer, and the residual sum, in one pass; with `residual` AND `out` the
 // new residual row is then normed again with (w2, b2) into `out`: the norm that the next sublayer begins with.
 // The row is kept in shared memory.
+// Sum over the block with one barrier: lanes by butterfly, then every thread adds the warps' sums in index order.
+// `scratch` is one of two arrays of 32 floats used in turn, so that a sum may begin while slow threads still read
+// the one before.
+__device__ __forceinline__ float block_sum_once(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < n_warps; ++w) total += scratch[w];
+  return total;
+}
+
 template <typename TO>
 __global__ void layernorm_affine_kernel(TO* __restrict__ out, float* __restrict__ residual, const float* __restrict__ x,
                                         int n_parts, size_t part_stride, const float* __restrict__ w,
                                         const float* __restrict__ b, const int* __restrict__ rows, int width, float eps,
                                         const float* __restrict__ w2, const float* __restrict__ b2) {
   extern __shared__ float row[];
-  __shared__ float scratch[33];
+  __shared__ float scratch[4][32];
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
@@ -212,13 +226,13 @@ __global__ void layernorm_affine_kernel(TO* __restrict__ out, float* __restrict_
     row[c] = v;
     acc += v;
   }
-  float mean = block_sum(acc, scratch) / (float)width;
+  float mean = block_sum_once(acc, scratch[0]) / (float)width;
   acc = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float d = row[c] - mean;
     acc = fmaf(d, d, acc);
   }
-  float inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  float inv = 1.0f / sqrtf(block_sum_once(acc, scratch[1]) / (float)width + eps);
   acc = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float y = ((row[c] - mean) * inv) * w[c] + (b != nullptr ? b[c] : 0.f);
@@ -232,13 +246,13 @@ __global__ void layernorm_affine_kernel(TO* __restrict__ out, float* __restrict_
     }
   }
   if (residual == nullptr || out == nullptr) return;
-  mean = block_sum(acc, scratch) / (float)width;
+  mean = block_sum_once(acc, scratch[2]) / (float)width;
   acc = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float d = row[c] - mean;
     acc = fmaf(d, d, acc);
   }
-  inv = 1.0f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+  inv = 1.0f / sqrtf(block_sum_once(acc, scratch[3]) / (float)width + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x)
     out[(size_t)r * width + c] = from_float<TO>(((row[c] - mean) * inv) * w2[c] + (b2 != nullptr ? b2[c] : 0.f));
 }

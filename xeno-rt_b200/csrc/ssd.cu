@@ -29,28 +29,63 @@ struct SsdArgs {
 // One block: one sequence, one head, `cols` value columns.  A column's state (n_state rows) is held in registers by
 // `parts` neighbouring lanes, R rows each (lane p holds rows p R .. p R + R - 1; rows beyond n_state stay zero);
 // the read-out's sum over rows is finished by a butterfly among those lanes, so its order is fixed.  Tiles of
-// `tile_tokens` tokens' b, c, x, step size and decay are staged in shared memory.
-template <int R>
+// `tile_tokens` tokens' b, c, x and raw step sizes are brought into shared memory by cp.async, two tiles in flight:
+// the next tile lands while this one is worked on.
+template <int BYTES>
+__device__ __forceinline__ void ssd_cp_async(float* smem, const float* global) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  if (BYTES == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(global) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(global) : "memory");
+}
+
+// VEC: 16-byte copies (n_state, cols, vdim and every row stride are multiples of 4 floats, every base 16-byte aligned).
+template <int R, bool VEC>
 __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
   extern __shared__ __align__(16) float tile[];
   pdl_trigger();
+  const int parts = a.parts, cols = a.cols, TT = a.tile_tokens, n_state = a.n_state, vdim = a.vdim;
+  const int padded = parts * R;
+  // a stage: b | c, each [TT][padded]; x [TT][cols]; raw step sizes [TT] (padded to 4); then step size and decay [TT] each
+  const int stage_floats = 2 * TT * padded + TT * cols + ((TT + 3) & ~3);
+  float* sdt = tile + 2 * stage_floats;
+  float* sdecay = sdt + TT;
+  if (padded != n_state || vdim % cols != 0)  // rows and columns beyond the head's stay zero
+    for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) tile[e] = 0.f;
   pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y;
   const int slot = a.seq_slot[s];
   const int begin = a.cu_seqlens[s], end = a.cu_seqlens[s + 1];
   if (slot < 0 || end <= begin) return;
-  const int parts = a.parts, cols = a.cols, TT = a.tile_tokens, n_state = a.n_state, vdim = a.vdim;
-  const int padded = parts * R;
+  __syncthreads();
   const int part = threadIdx.x % parts, jl = threadIdx.x / parts;
   const int col0 = blockIdx.z * cols, j = col0 + jl;
   const int g = h / a.heads_per_group;
   const bool live = j < vdim;
-  float* sb = tile;                  // [TT][padded]
-  float* sc = sb + TT * padded;      // [TT][padded]
-  float* sx = sc + TT * padded;      // [TT][cols]
-  float* sdt = sx + TT * cols;       // [TT] step size
-  float* sdecay = sdt + TT;          // [TT]
   const float rate = expf(a.a_log[h]), dt_bias = a.dt_bias[h], d_skip = a.d_skip[h];
+  constexpr int B = VEC ? 16 : 4, E = VEC ? 4 : 1;
+
+  auto issue = [&](int t0, int stage) {
+    float* sb = tile + stage * stage_floats;
+    float* sc = sb + TT * padded;
+    float* sx = sc + TT * padded;
+    float* sraw = sx + TT * cols;
+    const int nt = min(TT, end - t0);
+    const int per = n_state / E;
+    for (int e = threadIdx.x; e < nt * per; e += blockDim.x) {
+      const int tt = e / per, d = (e - tt * per) * E;
+      const size_t at = (size_t)(t0 + tt) * a.bc_stride + g * n_state + d;
+      ssd_cp_async<B>(sb + tt * padded + d, a.b + at);
+      ssd_cp_async<B>(sc + tt * padded + d, a.c + at);
+    }
+    const int xper = cols / E;
+    for (int e = threadIdx.x; e < nt * xper; e += blockDim.x) {
+      const int tt = e / xper, cc = (e - tt * xper) * E;
+      if (col0 + cc < vdim) ssd_cp_async<B>(sx + tt * cols + cc, a.x + (size_t)(t0 + tt) * a.x_stride + h * vdim + col0 + cc);
+    }
+    for (int tt = threadIdx.x; tt < nt; tt += blockDim.x)
+      ssd_cp_async<4>(sraw + tt, a.dt + (size_t)(t0 + tt) * a.dt_stride + h);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
 
   float S[R];
   float* sp = a.state + (((size_t)slot * a.n_heads + h) * vdim + j) * n_state;
@@ -59,21 +94,23 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
     const int row = part * R + i;
     S[i] = (live && row < n_state) ? sp[row] : 0.f;
   }
-  for (int t0 = begin; t0 < end; t0 += TT) {
+  issue(begin, 0);
+  int stage = 0;
+  for (int t0 = begin; t0 < end; t0 += TT, stage ^= 1) {
     const int nt = min(TT, end - t0);
+    if (t0 + TT < end) {
+      issue(t0 + TT, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
-    for (int e = threadIdx.x; e < nt * padded; e += blockDim.x) {
-      const int tt = e / padded, d = e - tt * padded;
-      const size_t t = (size_t)(t0 + tt);
-      sb[e] = d < n_state ? a.b[t * a.bc_stride + g * n_state + d] : 0.f;
-      sc[e] = d < n_state ? a.c[t * a.bc_stride + g * n_state + d] : 0.f;
-    }
-    for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
-      const int tt = e / cols, cc = e - tt * cols;
-      sx[e] = col0 + cc < vdim ? a.x[(size_t)(t0 + tt) * a.x_stride + h * vdim + col0 + cc] : 0.f;
-    }
+    const float* sb = tile + stage * stage_floats;
+    const float* sc = sb + TT * padded;
+    const float* sx = sc + TT * padded;
+    const float* sraw = sx + TT * cols;
     for (int tt = threadIdx.x; tt < nt; tt += blockDim.x) {
-      const float z = a.dt[(size_t)(t0 + tt) * a.dt_stride + h] + dt_bias;
+      const float z = sraw[tt] + dt_bias;
       const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
       sdt[tt] = dt;
       sdecay[tt] = expf(-rate * dt);
@@ -110,6 +147,7 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
       for (int o = parts >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
       if (part == 0 && live) a.out[(size_t)(t0 + tt) * a.n_heads * vdim + h * vdim + j] = fmaf(d_skip, xv, y);
     }
+    __syncthreads();  // the stage is written again by the copies of the tile after the next
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
@@ -171,12 +209,18 @@ XRT_EXPORT int xrt_ssd_scan(float* out, const float* x, int x_stride, const floa
   int threads = 128;
   while (threads > 32 && threads / parts >= 2 * vdim) threads /= 2;  // no more lanes than the columns need
   a.cols = threads / parts;
-  a.tile_tokens = max_new < 32 ? max_new : 32;
-  while (a.tile_tokens > 1 && (size_t)a.tile_tokens * (2 * parts * r + a.cols + 2) * sizeof(float) > 40 * 1024)
-    a.tile_tokens /= 2;
-  const size_t smem = ((size_t)a.tile_tokens * (2 * parts * r + a.cols + 2)) * sizeof(float);
+  a.tile_tokens = max_new < 16 ? max_new : 16;
+  auto floats = [&](int tt) { return (size_t)2 * (2 * tt * parts * r + tt * a.cols + ((tt + 3) & ~3)) + 2 * tt; };
+  while (a.tile_tokens > 1 && floats(a.tile_tokens) * sizeof(float) > 44 * 1024) a.tile_tokens /= 2;
+  const size_t smem = floats(a.tile_tokens) * sizeof(float);
+  const bool vec = n_state % 4 == 0 && a.cols % 4 == 0 && vdim % 4 == 0 && x_stride % 4 == 0 && bc_stride % 4 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
   dim3 grid(n_seqs, n_heads, (vdim + a.cols - 1) / a.cols);
-#define XRT_SSD(R) xrt::launch_kernel(xrt::ssd_scan_kernel<R>, grid, dim3(threads), smem, stream, a)
+#define XRT_SSD(R)                                                                                              \
+  do {                                                                                                          \
+    if (vec) xrt::launch_kernel(xrt::ssd_scan_kernel<R, true>, grid, dim3(threads), smem, stream, a);          \
+    else xrt::launch_kernel(xrt::ssd_scan_kernel<R, false>, grid, dim3(threads), smem, stream, a);             \
+  } while (0)
   if (r == 1) XRT_SSD(1);
   else if (r == 2) XRT_SSD(2);
   else if (r == 4) XRT_SSD(4);
