@@ -315,3 +315,47 @@ def test_experts_against_the_plain_experts(dtype, width, ff, experts, top, limit
     ops.moe_experts(out, _t(h).to(tdt), _t(w_in).to(tdt), _t(down.reshape(experts * width, ff)).to(tdt), _ints(ids),
                     _t(weights), ff, limit, 1.702)
     _close(out.sum(0).cpu().numpy(), want, 2e-5)  # the kernels keep 32-bit inside in both dtypes
+
+
+@pytest.mark.parametrize("width,ff,experts,top,n", [(64, 24, 6, 2, 230), (200, 72, 40, 1, 150), (256, 64, 8, 3, 333),
+                                                     (72, 136, 3, 3, 70)])
+def test_experts_of_many_tokens_sorted_by_expert_in_one_launch_a_product(width, ff, experts, top, n):
+    """The path of long steps in bfloat16: rows sorted by expert, both products for all experts in one launch each
+    (experts without a row, row counts that are no multiple of the tile, widths that are no multiple of the K step)."""
+    from xeno_rt_b200.csrc import ops
+    rng = np.random.default_rng(9)
+    limit = 1.5
+    h = _bf16(rng.normal(size=(n, width)))
+    gate, up = _bf16(rng.normal(0, 2 / np.sqrt(width), (experts, ff, width))), _bf16(rng.normal(0, 2 / np.sqrt(width), (experts, ff, width)))
+    down = _bf16(rng.normal(0, 1 / np.sqrt(ff), (experts, width, ff)))
+    usable = [e for e in range(experts) if e != 1] if experts > top + 1 else list(range(experts))  # expert 1 gets no row
+    ids = np.stack([rng.permutation(usable)[:top] for _ in range(n)]).astype(np.int32)
+    weights = rng.uniform(0.1, 1.0, size=(n, top)).astype(np.float32)
+    want = np.zeros((n, width))
+    for t in range(n):
+        for e, p in zip(ids[t], weights[t]):
+            want[t] += p * plain.expert(h[t].astype(np.float64), gate[e], up[e], down[e], limit)
+    bf = torch.bfloat16
+    w_in = _t(np.concatenate([np.concatenate([gate[e], up[e]]) for e in range(experts)])).to(bf)
+    w_out = _t(down.reshape(experts * width, ff)).to(bf)
+    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=DEV)
+    pos = torch.empty((n * top,), dtype=torch.int32, device=DEV)
+    row_token = torch.empty((n * top,), dtype=torch.int32, device=DEV)
+    ops.moe_group(offsets, pos, row_token, _ints(ids), experts)
+    counts = np.bincount(ids.reshape(-1), minlength=experts)
+    assert offsets.cpu().tolist() == [0] + np.cumsum(counts).tolist()
+    assert sorted(pos.cpu().tolist()) == list(range(n * top))
+    assert (row_token.cpu().numpy()[pos.cpu().numpy()] == np.repeat(np.arange(n), top)).all()
+    rows = torch.empty((n * top, width), dtype=bf, device=DEV)
+    ops.moe_gather(rows, _t(h).to(bf), row_token)
+    act = torch.empty((n * top, ff), dtype=bf, device=DEV)
+    y = torch.empty((n * top, width), device=DEV)
+    ops.moe_grouped_product(act, rows, w_in, offsets, experts, ff, limit, 1.702)
+    ops.moe_grouped_product(y, act, w_out, offsets, experts)
+    out = torch.empty((top, n, width), device=DEV)
+    ops.moe_combine(out, y, pos, _t(weights))
+    _close(out.sum(0).cpu().numpy(), want, 1.5e-2)  # the hidden units are rounded to bfloat16 between the products
+    # and the kernels of few tokens give the same up to that rounding
+    few = torch.empty((top, n, width), device=DEV)
+    ops.moe_experts(few, _t(h).to(bf), w_in, w_out, _ints(ids), _t(weights), ff, limit, 1.702)
+    _close(out.sum(0).cpu().numpy(), few.sum(0).cpu().numpy(), 1.5e-2)

@@ -38,6 +38,7 @@ _SIGNATURES = {
     "xrt_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_moe_experts": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
     "xrt_relu_squared": [_P, _P, _I, _I, _I, _P],
+    "xrt_moe_grouped_product": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "xrt_moe_group": [_P, _P, _P, _P, _I, _I, _I, _P],
     "xrt_moe_gather": [_P, _P, _P, _I, _I, _I, _P],
     "xrt_moe_activation": [_P, _P, _I, _I, _F, _F, _I, _P],
@@ -1014,6 +1015,22 @@ def moe_combine(out, y, pos, weights) -> None:
     _check(_kernels().xrt_moe_combine(_ptr(out, "out", torch.float32), _ptr(y, "y", torch.float32),
                                      _ptr(pos, "pos", torch.int32), _ptr(weights, "weights", torch.float32), n, width, top,
                                      _stream()), "moe_combine")
+
+
+def moe_grouped_product(out, a, w, offsets, n_experts: int, ff: int = 0, limit: float = 0.0, alpha: float = 0.0) -> None:
+    """One launch for all experts' products over rows sorted by expert (bfloat16): with ``ff`` the first product and
+    its activation, out bfloat16 [rows, ff] from a [rows, k] and w [experts * 2 * ff, k]; without, out float32
+    [rows, n] from a [rows, k] and w [experts * n, k].  ``offsets`` int32 [experts + 1] on the device."""
+    rows, k = a.shape
+    first = ff > 0
+    n = 2 * ff if first else out.shape[1]
+    if w.shape != (n_experts * n, k) or out.shape != (rows, ff if first else n) or offsets.numel() != n_experts + 1:
+        raise KernelError("moe_grouped_product: shapes do not fit")
+    _check(_kernels().xrt_moe_grouped_product(_ptr(out, "out", torch.bfloat16 if first else torch.float32),
+                                             _ptr(a, "a", torch.bfloat16), _ptr(w, "w", torch.bfloat16),
+                                             _ptr(offsets, "offsets", torch.int32), rows, int(n_experts), n, k, int(ff),
+                                             float(limit), float(alpha), 1 if first else 0, _stream()),
+           "moe_grouped_product")
 
 
 def relu_squared(out, x) -> None:

@@ -143,7 +143,8 @@ class RoutedExperts:
         """The chosen experts' weighted results, float32 [top, T, width]; their sum in index order is the result.
         A step of few tokens runs every (token, choice) pair in a block of its own, which streams that expert's
         matrices (a captured decode step: no size depends on the choices).  A step of many tokens sorts its rows by
-        expert and runs one pair of matrix products an expert; how many rows each expert has is read back once."""
+        expert; in bfloat16 two launches then serve all experts (csrc/moe_grouped.cu), in float32 every expert's rows
+        go through the library's product, for which the experts' row counts are read back once."""
         n = h.shape[0]
         ids, weights = self.route(h)
         out = torch.empty((self.top, n, self.width), dtype=torch.float32, device=h.device)
@@ -157,15 +158,23 @@ class RoutedExperts:
         ops.moe_group(offsets, pos, row_token, ids, self.experts)
         rows = torch.empty((pairs, self.width), dtype=h.dtype, device=h.device)
         ops.moe_gather(rows, h, row_token)
-        bounds = offsets.tolist()  # the one wait of the host for the device in this part
-        act = torch.empty((pairs, self.inner), dtype=h.dtype, device=h.device)
-        y = torch.zeros((pairs, self.width), dtype=torch.float32, device=h.device)
-        for e in range(self.experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                gate_up = linear(rows[lo:hi], self.w_in[e * 2 * self.inner:(e + 1) * 2 * self.inner], out_dtype=torch.float32)
-                ops.moe_activation(act[lo:hi], gate_up, self.limit, self.alpha)
-                linear(act[lo:hi], self.w_out[e * self.width:(e + 1) * self.width], accumulate_into=y[lo:hi])
+        if h.dtype == torch.bfloat16 and self.width % 8 == 0 and self.inner % 8 == 0:
+            # all experts in one launch a product: the blocks find their expert from the offsets on the device
+            act = torch.empty((pairs, self.inner), dtype=h.dtype, device=h.device)
+            y = torch.empty((pairs, self.width), dtype=torch.float32, device=h.device)
+            ops.moe_grouped_product(act, rows, self.w_in, offsets, self.experts, self.inner, self.limit, self.alpha)
+            ops.moe_grouped_product(y, act, self.w_out, offsets, self.experts)
+        else:
+            bounds = offsets.tolist()  # here the host waits for the device: how many rows each expert has
+            act = torch.empty((pairs, self.inner), dtype=h.dtype, device=h.device)
+            y = torch.zeros((pairs, self.width), dtype=torch.float32, device=h.device)
+            for e in range(self.experts):
+                lo, hi = bounds[e], bounds[e + 1]
+                if hi > lo:
+                    gate_up = linear(rows[lo:hi], self.w_in[e * 2 * self.inner:(e + 1) * 2 * self.inner],
+                                     out_dtype=torch.float32)
+                    ops.moe_activation(act[lo:hi], gate_up, self.limit, self.alpha)
+                    linear(act[lo:hi], self.w_out[e * self.width:(e + 1) * self.width], accumulate_into=y[lo:hi])
         ops.moe_combine(out, y, pos, weights)
         return out
 
