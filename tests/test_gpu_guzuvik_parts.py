@@ -70,7 +70,7 @@ def test_pair_embedding_in_portions_with_its_state_and_a_slot_used_again(buckets
 
 
 # ------------------------------------------------------------------------------------------------ norms
-@pytest.mark.parametrize("width", [36, 320, 1500])
+@pytest.mark.parametrize("width", [36, 320, 1500, 3000, 5000])
 def test_layer_norm_with_a_bias_alone_and_added_to_the_stream(width):
     from xeno_rt_b200.csrc import ops
     rng = np.random.default_rng(2)

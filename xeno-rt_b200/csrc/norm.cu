@@ -257,6 +257,84 @@ __global__ void layernorm_affine_kernel(TO* __restrict__ out, float* __restrict_
     out[(size_t)r * width + c] = from_float<TO>(((row[c] - mean) * inv) * w2[c] + (b2 != nullptr ? b2[c] : 0.f));
 }
 
+// The same for rows of up to 256 * ITEMS floats, held in registers: the weights and biases of both norms are asked
+// for before the wait for the kernel before, the row and the residual together after it, so that a row of a decode
+// step costs two trips to memory instead of six in a row.
+template <typename TO, int ITEMS>
+__global__ void __launch_bounds__(256)
+layernorm_affine_rows_kernel(TO* __restrict__ out, float* __restrict__ residual, const float* __restrict__ x, int n_parts,
+                             size_t part_stride, const float* __restrict__ w, const float* __restrict__ b,
+                             const int* __restrict__ rows, int width, float eps, const float* __restrict__ w2,
+                             const float* __restrict__ b2) {
+  __shared__ float scratch[4][32];
+  pdl_trigger();
+  float wv[ITEMS], bv[ITEMS], w2v[ITEMS], b2v[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int c = threadIdx.x + i * 256;
+    const bool in = c < width;
+    wv[i] = in ? w[c] : 0.f;
+    bv[i] = in && b != nullptr ? b[c] : 0.f;
+    w2v[i] = in && w2 != nullptr ? w2[c] : 0.f;
+    b2v[i] = in && b2 != nullptr ? b2[c] : 0.f;
+  }
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows != nullptr ? rows[r] : r;
+  const float* xr = x + (size_t)src * width;
+  float v[ITEMS], res[ITEMS];
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = 0.f;
+    res[i] = 0.f;
+    if (c < width) {
+      v[i] = xr[c];
+      for (int p = 1; p < n_parts; ++p) v[i] += xr[p * part_stride + c];
+      if (residual != nullptr) res[i] = residual[(size_t)r * width + c];
+    }
+    acc += v[i];
+  }
+  float mean = block_sum_once(acc, scratch[0]) / (float)width;
+  acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const float d = threadIdx.x + i * 256 < width ? v[i] - mean : 0.f;
+    acc = fmaf(d, d, acc);
+  }
+  float inv = 1.0f / sqrtf(block_sum_once(acc, scratch[1]) / (float)width + eps);
+  acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < width) {
+      const float y = ((v[i] - mean) * inv) * wv[i] + bv[i];
+      if (residual != nullptr) {
+        v[i] = res[i] + y;
+        residual[(size_t)r * width + c] = v[i];
+        acc += v[i];
+      } else {
+        out[(size_t)r * width + c] = from_float<TO>(y);
+      }
+    }
+  }
+  if (residual == nullptr || out == nullptr) return;
+  mean = block_sum_once(acc, scratch[2]) / (float)width;
+  acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const float d = threadIdx.x + i * 256 < width ? v[i] - mean : 0.f;
+    acc = fmaf(d, d, acc);
+  }
+  inv = 1.0f / sqrtf(block_sum_once(acc, scratch[3]) / (float)width + eps);
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < width) out[(size_t)r * width + c] = from_float<TO>(((v[i] - mean) * inv) * w2v[i] + b2v[i]);
+  }
+}
+
 }  // namespace xrt
 
 XRT_EXPORT int xrt_layernorm_affine(void* out, float* residual, const float* x, int n_parts, long long part_stride,
@@ -269,6 +347,20 @@ XRT_EXPORT int xrt_layernorm_affine(void* out, float* residual, const float* x, 
   if (n_rows == 0) return XRT_OK;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   const size_t smem = (size_t)width * sizeof(float);
+  if (width <= 256 * 16) {
+    XRT_DISPATCH_DTYPE(out_dtype, TO, {
+      if (width <= 256 * 4)
+        xrt::launch_kernel(xrt::layernorm_affine_rows_kernel<TO, 4>, dim3(n_rows), dim3(256), 0, stream, (TO*)out, residual, x,
+                           n_parts, (size_t)part_stride, weight, bias, rows, width, eps, weight2, bias2);
+      else if (width <= 256 * 8)
+        xrt::launch_kernel(xrt::layernorm_affine_rows_kernel<TO, 8>, dim3(n_rows), dim3(256), 0, stream, (TO*)out, residual, x,
+                           n_parts, (size_t)part_stride, weight, bias, rows, width, eps, weight2, bias2);
+      else
+        xrt::launch_kernel(xrt::layernorm_affine_rows_kernel<TO, 16>, dim3(n_rows), dim3(256), 0, stream, (TO*)out, residual, x,
+                           n_parts, (size_t)part_stride, weight, bias, rows, width, eps, weight2, bias2);
+    });
+    return xrt::launch_status();
+  }
   XRT_DISPATCH_DTYPE(out_dtype, TO, {
     auto kernel = xrt::layernorm_affine_kernel<TO>;
     if (smem > 48 * 1024) {
