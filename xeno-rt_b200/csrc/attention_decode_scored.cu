@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(DS_WARPS * 32) attention_decode_scored_kernel(
       for (int g = 0; g < G; ++g) s[g] = 0.f;
       if (live) {
         const __nv_bfloat16* kr = a.k_pool + row;
+#pragma unroll 4
         for (int d = 0; d < hd; d += 8) {
           const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
           const __nv_bfloat162* kk = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -113,8 +114,10 @@ __global__ void __launch_bounds__(DS_WARPS * 32) attention_decode_scored_kernel(
 #pragma unroll
         for (int j = 0; j < 2 * PAIRS; ++j) acc[g][j] *= corr;
       }
-      const int n_live = min(32, v_end - v0);
-      for (int kk = 0; kk < n_live; ++kk) {
+      // all 32 keys of the tile, several keys' loads in flight: a lane beyond the range holds weight 0 and the row
+      // of the token's own key, which is there to be read
+#pragma unroll 8
+      for (int kk = 0; kk < 32; ++kk) {
         const size_t vrow = __shfl_sync(0xffffffffu, (unsigned long long)row, kk);
         float pk[G];
 #pragma unroll
