@@ -225,3 +225,33 @@ def test_trace_replay_as_a_user_runs_it(cases, tmp_path, dtype):
             at += len(e["want"])
     for i in range(len(prompts)):
         _check(np.concatenate(got[i]), want[i][0], want[i][1], dtype, rows[i])
+
+
+def test_decode_steps_of_many_sequences_sort_their_experts_rows_inside_the_captured_step(cases):
+    """11 sequences a step (16 rows with padding): enough (token, choice) pairs an expert for the grouped products,
+    which run inside the captured step with the row counts staying on the device; the padding rows count as rows of
+    some expert and change nothing."""
+    from xeno_rt_b200.engine import StepEntry
+    folder, config, weights = cases["wide"]
+    engine = _engine(folder, "bfloat16", 64 * 16)
+    assert engine.use_graphs and engine.model.graph_safe
+    lengths = [3, 9, 17, 5, 11, 2, 8, 13, 4, 6, 21]
+    decode = 6
+    prompts = random_prompts(config["vocab"], [k + decode for k in lengths], seed=12)
+    want = [_plain(config, weights, p, "bfloat16") for p in prompts]
+    slots = [engine.open_slot() for _ in prompts]
+    got = [[] for _ in prompts]
+    out = engine.step([StepEntry(s, p[:k], list(range(k))) for s, p, k in zip(slots, prompts, lengths)]).cpu().numpy()
+    at = 0
+    for i, k in enumerate(lengths):
+        got[i].append(out[at:at + k])
+        at += k
+    for step in range(decode):
+        out = engine.step([StepEntry(slots[i], [prompts[i][lengths[i] + step]], [0]) for i in range(len(prompts))]).cpu().numpy()
+        for i in range(len(prompts)):
+            got[i].append(out[i:i + 1])
+    for i in range(len(prompts)):
+        _check(np.concatenate(got[i]), want[i][0], want[i][1], "bfloat16")
+        engine.close_slot(slots[i])
+    engine.check_errors()
+    engine.cache.check()

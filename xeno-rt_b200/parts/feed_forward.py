@@ -141,24 +141,27 @@ class RoutedExperts:
 
     def apply(self, h, ctx):
         """The chosen experts' weighted results, float32 [top, T, width]; their sum in index order is the result.
-        A step of few tokens runs every (token, choice) pair in a block of its own, which streams that expert's
-        matrices (a captured decode step: no size depends on the choices).  A step of many tokens sorts its rows by
-        expert; in bfloat16 two launches then serve all experts (csrc/moe_grouped.cu), in float32 every expert's rows
-        go through the library's product, for which the experts' row counts are read back once."""
+        A step of few tokens runs every (token, choice) pair by itself, streaming that expert's matrices.  A step of
+        many tokens (prompts, and decode steps of many sequences) sorts its rows by expert; in bfloat16 two launches
+        then serve all experts with the row counts staying on the device (csrc/moe_grouped.cu: fit for a captured
+        step), in float32 every expert's rows go through the library's product, for which the row counts are read back
+        once (prompts only)."""
         n = h.shape[0]
         ids, weights = self.route(h)
         out = torch.empty((self.top, n, self.width), dtype=torch.float32, device=h.device)
-        if getattr(ctx, "captured", False) or ctx.all_single or n * self.top < self.GROUPED_FROM * self.experts:
+        pairs = n * self.top
+        one_launch = h.dtype == torch.bfloat16 and self.width % 8 == 0 and self.inner % 8 == 0
+        fixed_shapes = getattr(ctx, "captured", False) or ctx.all_single  # no read-back inside such a step
+        if pairs < self.GROUPED_FROM * self.experts or (fixed_shapes and not one_launch):
             ops.moe_experts(out, h, self.w_in, self.w_out, ids, weights, self.inner, self.limit, self.alpha)
             return out
-        pairs = n * self.top
         offsets = torch.empty((self.experts + 1,), dtype=torch.int32, device=h.device)
         pos = torch.empty((pairs,), dtype=torch.int32, device=h.device)
         row_token = torch.empty((pairs,), dtype=torch.int32, device=h.device)
         ops.moe_group(offsets, pos, row_token, ids, self.experts)
         rows = torch.empty((pairs, self.width), dtype=h.dtype, device=h.device)
         ops.moe_gather(rows, h, row_token)
-        if h.dtype == torch.bfloat16 and self.width % 8 == 0 and self.inner % 8 == 0:
+        if one_launch:
             # all experts in one launch a product: the blocks find their expert from the offsets on the device
             act = torch.empty((pairs, self.inner), dtype=h.dtype, device=h.device)
             y = torch.empty((pairs, self.width), dtype=torch.float32, device=h.device)
