@@ -27,7 +27,7 @@ struct SsdArgs {
 };
 
 // One block: one sequence, one head, `cols` value columns.  A column's state (n_state rows) is held in registers by
-// `parts` neighbouring lanes, R rows each (lane p holds rows p R .. p R + R - 1; rows beyond n_state stay zero);
+// `parts` neighbouring lanes, R rows each (which rows: `row_of` in the kernel; rows beyond n_state stay zero);
 // the read-out's sum over rows is finished by a butterfly among those lanes, so its order is fixed.  Tiles of
 // `tile_tokens` tokens' b, c, x and raw step sizes are brought into shared memory by cp.async, two tiles in flight:
 // the next tile lands while this one is worked on.
@@ -63,6 +63,9 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
   const bool live = j < vdim;
   const float rate = expf(a.a_log[h]), dt_bias = a.dt_bias[h], d_skip = a.d_skip[h];
   constexpr int B = VEC ? 16 : 4, E = VEC ? 4 : 1;
+  // the lane's i-th row: with four rows or more a lane, every parts-th group of four (the lanes of a column then read
+  // neighbouring 16 bytes of b, c and the state: whole lines, all banks), else R neighbouring rows
+  auto row_of = [&](int i) { return R % 4 == 0 ? 4 * ((i >> 2) * parts + part) + (i & 3) : part * R + i; };
 
   auto issue = [&](int t0, int stage) {
     float* sb = tile + stage * stage_floats;
@@ -91,7 +94,7 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
   float* sp = a.state + (((size_t)slot * a.n_heads + h) * vdim + j) * n_state;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int row = part * R + i;
+    const int row = row_of(i);
     S[i] = (live && row < n_state) ? sp[row] : 0.f;
   }
   issue(begin, 0);
@@ -124,8 +127,8 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
       if (R % 4 == 0) {  // a lane's rows of b and c as whole 16 bytes
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
-          const float4 b4 = *reinterpret_cast<const float4*>(sb + tt * padded + part * R + i);
-          const float4 c4 = *reinterpret_cast<const float4*>(sc + tt * padded + part * R + i);
+          const float4 b4 = *reinterpret_cast<const float4*>(sb + tt * padded + row_of(i));
+          const float4 c4 = *reinterpret_cast<const float4*>(sc + tt * padded + row_of(i));
           bt[i] = b4.x; bt[i + 1] = b4.y; bt[i + 2] = b4.z; bt[i + 3] = b4.w;
           ct[i] = c4.x; ct[i + 1] = c4.y; ct[i + 2] = c4.z; ct[i + 3] = c4.w;
         }
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int row = part * R + i;
+    const int row = row_of(i);
     if (live && row < n_state) sp[row] = S[i];
   }
 }
