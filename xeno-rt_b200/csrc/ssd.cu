@@ -74,11 +74,20 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(const SsdArgs a) {
     float* sraw = sx + TT * cols;
     const int nt = min(TT, end - t0);
     const int per = n_state / E;
-    for (int e = threadIdx.x; e < nt * per; e += blockDim.x) {
-      const int tt = e / per, d = (e - tt * per) * E;
-      const size_t at = (size_t)(t0 + tt) * a.bc_stride + g * n_state + d;
-      ssd_cp_async<B>(sb + tt * padded + d, a.b + at);
-      ssd_cp_async<B>(sc + tt * padded + d, a.c + at);
+    if (blockDim.x % per == 0) {  // a thread keeps its piece of the row and steps down the tokens: no division a copy
+      const int d = (threadIdx.x % per) * E;
+      for (int tt = threadIdx.x / per; tt < nt; tt += blockDim.x / per) {
+        const size_t at = (size_t)(t0 + tt) * a.bc_stride + g * n_state + d;
+        ssd_cp_async<B>(sb + tt * padded + d, a.b + at);
+        ssd_cp_async<B>(sc + tt * padded + d, a.c + at);
+      }
+    } else {
+      for (int e = threadIdx.x; e < nt * per; e += blockDim.x) {
+        const int tt = e / per, d = (e - tt * per) * E;
+        const size_t at = (size_t)(t0 + tt) * a.bc_stride + g * n_state + d;
+        ssd_cp_async<B>(sb + tt * padded + d, a.b + at);
+        ssd_cp_async<B>(sc + tt * padded + d, a.c + at);
+      }
     }
     const int xper = cols / E;
     for (int e = threadIdx.x; e < nt * xper; e += blockDim.x) {
