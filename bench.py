@@ -433,7 +433,7 @@ def run_attention_only(args) -> int:
     import xeno_rt_b200  # noqa: F401
     from xeno_rt_b200.cache import BLOCK_TOKENS
     from xeno_rt_b200.csrc import ops
-    from xeno_rt_b200.parts.attention_bf16 import FUSED_COMBINE_MAX, decode_split, visible_span
+    from xeno_rt_b200.parts.attention_bf16 import FUSED_COMBINE_MAX, decode_split, scored_decode_split, visible_span
 
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device: bench.py needs a B200"}))
@@ -458,9 +458,16 @@ def run_attention_only(args) -> int:
     chunk, n_splits = decode_split(batch, kv_heads, span, ops.device_state(dev)[2])
     fused = batch * kv_heads <= FUSED_COMBINE_MAX
 
+    if args.scored:  # the single-token kernel of layers with score options: kept first keys, a cap, a distance slope
+        chunk, n_splits = scored_decode_split(batch, kv_heads, context, window, 4, ops.device_state(dev)[2])
+
     def launch():
-        ops.attention_decode(out, q, k, v, slot, pos, table, heads, kv_heads, head_dim, 1 / math.sqrt(head_dim), window,
-                             chunk, n_splits, fused=fused)
+        if args.scored:
+            ops.attention_decode_scored(out, q, k, v, slot, pos, table, heads, kv_heads, head_dim, 1 / math.sqrt(head_dim),
+                                        window, 4, 50.0, 8.0, chunk, n_splits)
+        else:
+            ops.attention_decode(out, q, k, v, slot, pos, table, heads, kv_heads, head_dim, 1 / math.sqrt(head_dim), window,
+                                 chunk, n_splits, fused=fused)
 
     for _ in range(max(3, args.warmup)):
         launch()
@@ -479,7 +486,7 @@ def run_attention_only(args) -> int:
     us = start.elapsed_time(stop) / repeats * 1000
     keys = min(context, window + BLOCK_TOKENS - 1) if window > 0 else context
     read = batch * keys * kv_heads * head_dim * 2 * 2
-    print(json.dumps({"only": "attention", "us": round(us, 2), "batch": batch, "context": context, "window": window,
+    print(json.dumps({"only": "attention", "scored": bool(args.scored), "us": round(us, 2), "batch": batch, "context": context, "window": window,
                       "keys_a_split": chunk, "splits": n_splits, "heads": heads, "kv_heads": kv_heads,
                       "head_dim": head_dim, "gbs_upper": round(read / us / 1000, 1),
                       "flush": "none: launches back to back; cache of %d MB" % (2 * k.numel() * 2 // 2**20)}))
@@ -585,6 +592,9 @@ def main() -> int:
                              "--prefill-tokens, --batch, --context, --steps as for the headline run)")
     parser.add_argument("--design-sizes", default="", help="--design: which sizes, with commas (default: all of 2k, 4k)")
     parser.add_argument("--window", type=int, default=0, help="--only attention: keys a token sees (0 = all)")
+    parser.add_argument("--scored", action="store_true",
+                        help="--only attention: the single-token kernel of layers with score options (4 kept first keys, "
+                             "cap 50, distance slopes) instead of the plain decode attention")
     parser.add_argument("--splits-from", default="window", choices=["window", "context"],
                         help="--only attention with a window: cut the splits from the window's span (what the engine "
                              "does) or from the whole context (what a layer without a window gets)")

@@ -92,10 +92,10 @@ def decode_from_qkv(out, qkv, k_offset, v_offset, q_norm, k_norm, eps, cos_sin, 
 def scored_decode_split(n_tokens: int, n_kv_heads: int, context: int, window: int, keep_first: int, sms: int):
     """(keys a split, splits) for the single-token kernel of the scored layers: the most keys a token can see (the
     window or the context, and the kept first keys) in stretches of a multiple of 128 keys (32 a warp), as many as
-    give every multiprocessor about two blocks."""
+    give every multiprocessor about four blocks (what its registers hold)."""
     most = (min(window, context) if window > 0 else context) + (keep_first if window > 0 else 0)
     pairs = max(1, n_tokens * n_kv_heads)
-    splits = max(1, min(-(-2 * sms // pairs), -(-most // 128), 64))
+    splits = max(1, min(-(-4 * sms // pairs), -(-most // 128), 64))
     chunk = -(-(-(-most // splits)) // 128) * 128
     return chunk, -(-most // chunk)
 
